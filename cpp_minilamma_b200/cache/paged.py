@@ -4,7 +4,8 @@
   group, the pages that hold its keys and values.  Slots are handed out by `acquire`,
   given back by `release`, and used again by later batches.
 * A **page** holds PAGE consecutive positions of one sequence for every cache entry of
-  one group: tensors `k, v [entries, pages, kv_heads, PAGE, head_dim]`.  Pages come from a
+  one group: tensors `k, v [entries, pages, kv_heads, PAGE, head_dim]` (the values' last dimension is
+  the group's `v_head_dim` where a mixer gives keys and values head sizes of their own).  Pages come from a
   free list per group, so a budget of N tokens (each sequence rounded up to whole pages)
   is all the memory the cache ever needs, however the tokens are spread over sequences.
 * A **group** gathers the schedule entries whose mixers declare the same need
@@ -112,7 +113,7 @@ class CacheGroup:
         # one page and one block-table row beyond those that are handed out: the padding slot's (SequenceCache.pad_slot)
         shape = (len(entries), n_pages + 1, need.n_kv_heads, PAGE, need.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        self.v = torch.empty((*shape[:-1], need.v_head_dim or need.head_dim), dtype=dtype, device=device)
         self.table_host = np.full((n_slots + 1, max_blocks), -1, dtype=np.int32)
         self.table_host[n_slots, 0] = n_pages
         self.table_dev = torch.from_numpy(self.table_host.copy()).to(device)
@@ -350,7 +351,8 @@ class SequenceCache:
 
     def kv_bytes_per_token(self) -> int:
         width = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * width for g in self.groups)
+        return sum(len(g.entries) * g.need.n_kv_heads * (g.need.head_dim + (g.need.v_head_dim or g.need.head_dim)) * width
+                   for g in self.groups)
 
     def read_kv(self, entry: int, slot: int, length: Optional[int] = None):
         """Keys and values of a sequence as [length, kv_heads, head_dim] (for tests)."""

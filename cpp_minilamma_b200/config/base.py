@@ -1,6 +1,7 @@
 """Typed configuration base and the architecture registry.
 
-A model folder's `config.json` names its architecture in `architectures[0]`.
+A model folder's `config.json` names its architecture in `architectures[0]` (or, as a plain
+string, in `architecture`).
 The registry maps that name to a configuration class (which parses and checks
 the architecture's own keys) and to a builder (which turns the typed
 configuration into a `ModelSpec`: parts chosen layer by layer plus the order in
@@ -64,6 +65,9 @@ def lookup_architecture(name: str):
 
 
 def architecture_of(raw: Dict[str, Any]) -> str:
+    """The design's name: `architectures` (a list with one name) or `architecture` (the name itself)."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a list with exactly one name")

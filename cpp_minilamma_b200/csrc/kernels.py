@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 27
+ABI_VERSION = 28
 MAX_TOP_K = 1024
 
 
@@ -406,21 +406,32 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, row_norm: Optio
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
-                eps: float, rows: Optional[torch.Tensor] = None) -> None:
-    """x += delta (float32 residual, in place); out = rmsnorm(x) * weight.
+                eps: float, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> None:
+    """x += delta (+ delta2) (float32 residual, in place); out = rmsnorm(x) * weight.
 
     With `rows` (int32 [n]) only those rows of x are normalised into out [n, D] and x is
-    left unchanged."""
+    left unchanged.  `delta2`: the output of a second part that read the same norm as `delta`'s.
+    out may be float32 whatever the deltas' dtype, and may be x itself."""
     _need(x, "rmsnorm x", torch.float32, 2)
     _need(weight, "rmsnorm weight", torch.float32, 1)
     _need(out, "rmsnorm out", None, 2)
     width = x.shape[1]
     if weight.shape[0] != width or out.shape[1] != width:
         raise KernelError(f"rmsnorm: widths differ: x {width}, weight {weight.shape[0]}, out {out.shape[1]}")
+    delta_dtype = out.dtype
     if delta is not None:
-        _need(delta, "rmsnorm delta", out.dtype, 2)
+        _need(delta, "rmsnorm delta", None, 2)
+        delta_dtype = delta.dtype
         if delta.shape != x.shape:
             raise KernelError(f"rmsnorm: delta {tuple(delta.shape)} differs from x {tuple(x.shape)}")
+    if delta2 is not None:
+        if delta is None:
+            raise KernelError("rmsnorm: a second delta without a first")
+        _need(delta2, "rmsnorm delta2", delta.dtype, 2)
+        if delta2.shape != x.shape:
+            raise KernelError(f"rmsnorm: delta2 {tuple(delta2.shape)} differs from x {tuple(x.shape)}")
+    if delta_dtype != out.dtype and not (delta_dtype == torch.bfloat16 and out.dtype == torch.float32):
+        raise KernelError(f"rmsnorm: delta {delta_dtype} with out {out.dtype}")
     if rows is not None:
         _need(rows, "rmsnorm rows", torch.int32, 1)
         n_rows = rows.shape[0]
@@ -428,9 +439,9 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         n_rows = x.shape[0]
     if out.shape[0] != n_rows:
         raise KernelError(f"rmsnorm: out has {out.shape[0]} rows, expected {n_rows}")
-    _check(lib().mll_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
-                                 dtype_code(out.dtype), ctypes.c_int(n_rows), ctypes.c_int(width),
-                                 ctypes.c_float(eps), _stream()), "rmsnorm")
+    _check(lib().mll_add2_rmsnorm(_ptr(x), _ptr(delta), _ptr(delta2), _ptr(weight), _ptr(out), _ptr(rows),
+                                  dtype_code(delta_dtype), dtype_code(out.dtype), ctypes.c_int(n_rows),
+                                  ctypes.c_int(width), ctypes.c_float(eps), _stream()), "rmsnorm")
 
 
 def apply_row_norm(values: torch.Tensor, row_norm: RowNorm, out: torch.Tensor) -> None:
@@ -766,3 +777,187 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, requ
                             ctypes.c_float(temperature), ctypes.c_int(top_k),
                             ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _ptr(request), _ptr(step),
                             _ptr(tokens), _ptr(status), _stream()), "sample")
+
+
+# --------------------------------------------------------------------------- #
+# attention with head sizes of its own for keys and values, chunks, partial rotation
+# --------------------------------------------------------------------------- #
+def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out,
+                            k_cache, v_cache, n_heads: int, n_kv_heads: int, d: int, dv: int, rot: int,
+                            interleaved: bool, eps: float) -> None:
+    """qkv [T, ld] (q heads of d, k heads of d, v heads of dv): q and k each divided by the root mean square of
+    their whole projection and multiplied by `q_weight` / `k_weight` (float32; both None: no norm), the first
+    `rot` dimensions of every q and k head rotated, q to `q_out` [T, Hq * d], k and v into the cache pages
+    ([pages, Hk, PAGE, d] and [pages, Hk, PAGE, dv])."""
+    _need(qkv, "local attention qkv", None, 2)
+    _need(q_out, "local attention q", qkv.dtype, 2)
+    _need(k_cache, "local attention k cache", qkv.dtype, 4)
+    _need(v_cache, "local attention v cache", qkv.dtype, 4)
+    n = qkv.shape[0]
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, d) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, dv):
+        raise KernelError(f"local attention: caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not fit "
+                          f"{n_kv_heads} heads of {d} / {dv}")
+    if tuple(q_out.shape) != (n, n_heads * d):
+        raise KernelError(f"local attention: q out {tuple(q_out.shape)}, expected {(n, n_heads * d)}")
+    for name, w, size in (("q", q_weight, n_heads * d), ("k", k_weight, n_kv_heads * d)):
+        if w is not None:
+            _need(w, f"local attention {name} norm weight", torch.float32, 1)
+            if w.shape[0] != size:
+                raise KernelError(f"local attention: {name} norm weight of {w.shape[0]}, expected {size}")
+    if rot:
+        _need(cos, "local attention cos", torch.float32, 2)
+        _need(sin, "local attention sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError(f"local attention: rotary table {tuple(cos.shape)} for {rot} rotated dimensions")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot)):
+        _need(t, f"local attention {name}", torch.int32, 1)
+    _need(block_table, "local attention block table", torch.int32, 2)
+    _check(lib().mll_local_attention_prepare(
+        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos if rot else None), _ptr(sin if rot else None),
+        _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(block_table), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+        dtype_code(qkv.dtype), ctypes.c_int(n), ctypes.c_int(qkv.shape[1]), ctypes.c_int(n_heads),
+        ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(rot), ctypes.c_int(int(interleaved)),
+        ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), _stream()), "local_attention_prepare")
+
+
+def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_heads: int, n_kv_heads: int,
+                    d: int, dv: int, chunk: int, window: int, scale: float) -> None:
+    """out [T, Hq * dv] = softmax(scale * q . k) v over the keys j <= i of the query's own chunk (j // chunk ==
+    i // chunk; chunk 0: all) and window (j > i - window; 0: none); the step's own keys are in the cache already."""
+    _need(q, "local attention q", None, 2)
+    _need(out, "local attention out", q.dtype, 2)
+    _need(k_cache, "local attention k cache", q.dtype, 4)
+    _need(v_cache, "local attention v cache", q.dtype, 4)
+    n = q.shape[0]
+    if tuple(q.shape) != (n, n_heads * d) or tuple(out.shape) != (n, n_heads * dv):
+        raise KernelError(f"local attention: q {tuple(q.shape)} / out {tuple(out.shape)} for {n_heads} heads of {d} / {dv}")
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, d) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, dv):
+        raise KernelError("local attention: the caches do not fit the head sizes")
+    _check(lib().mll_local_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(block_table),
+        _ptr(out), dtype_code(q.dtype), ctypes.c_int(n), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk), ctypes.c_int(window),
+        ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), _stream()), "local_attention")
+
+
+# --------------------------------------------------------------------------- #
+# mixers with a matrix-valued state per sequence and head
+# --------------------------------------------------------------------------- #
+def retention_prepare(proj, cos, sin, tok_pos, q, k, v, n_heads: int, d: int, dv: int, rot: int, interleaved: bool,
+                      k_scale: float) -> None:
+    """proj [T, ld] (q heads of d, k heads of d, v heads of dv, ...) -> float32 q, k [T, H, d] with the first `rot`
+    dimensions of every head rotated and k * k_scale, v [T, H, dv]."""
+    _need(proj, "retention proj", None, 2)
+    n = proj.shape[0]
+    for name, t, width in (("q", q, n_heads * d), ("k", k, n_heads * d), ("v", v, n_heads * dv)):
+        _need(t, f"retention {name}", torch.float32, 2)
+        if tuple(t.shape) != (n, width):
+            raise KernelError(f"retention prepare: {name} {tuple(t.shape)}, expected {(n, width)}")
+    if rot:
+        _need(cos, "retention cos", torch.float32, 2)
+        _need(sin, "retention sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError(f"retention prepare: rotary table {tuple(cos.shape)} for {rot} rotated dimensions")
+    _need(tok_pos, "retention tok_pos", torch.int32, 1)
+    _check(lib().mll_retention_prepare(
+        _ptr(proj), _ptr(cos if rot else None), _ptr(sin if rot else None), _ptr(tok_pos), _ptr(q), _ptr(k), _ptr(v),
+        dtype_code(proj.dtype), ctypes.c_int(n), ctypes.c_int(proj.shape[1]), ctypes.c_int(n_heads), ctypes.c_int(d),
+        ctypes.c_int(dv), ctypes.c_int(rot), ctypes.c_int(int(interleaved)), ctypes.c_float(k_scale), _stream()),
+        "retention_prepare")
+
+
+def delta_prepare(proj, rate, conv_w, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, v, g, beta,
+                  n_heads: int, n_kv_heads: int, d: int, dv: int, taps: int, unit_eps: float) -> None:
+    """The inputs of the gated delta rule from the projections of a step (see csrc/recurrent.cu): proj [T, ld]
+    holds q, k (G heads of d), v (H heads of dv) and beta's pre-activation (H); rate float32 [T, >= H * d] the
+    decay's; conv_w float32 [C, taps]; conv_state float32 [slots, taps - 1, C]."""
+    _need(proj, "delta proj", None, 2)
+    _need(rate, "delta rate", torch.float32, 2)
+    _need(conv_w, "delta conv weights", torch.float32, 2)
+    _need(conv_state, "delta conv state", torch.float32, 3)
+    _need(a_log, "delta A_log", torch.float32, 1)
+    _need(dt_bias, "delta dt_bias", torch.float32, 1)
+    n = proj.shape[0]
+    C = 2 * n_kv_heads * d + n_heads * dv
+    if tuple(conv_w.shape) != (C, taps) or tuple(conv_state.shape[1:]) != (max(taps - 1, 0), C):
+        raise KernelError(f"delta prepare: conv weights {tuple(conv_w.shape)} / state {tuple(conv_state.shape)} "
+                          f"for {C} channels of {taps} taps")
+    if a_log.shape[0] != n_heads or dt_bias.shape[0] != n_heads * d or rate.shape[0] != n:
+        raise KernelError("delta prepare: A_log, dt_bias or rate of the wrong size")
+    for name, t, width in (("q", q, n_kv_heads * d), ("k", k, n_kv_heads * d), ("v", v, n_heads * dv),
+                           ("g", g, n_heads * d), ("beta", beta, n_heads)):
+        _need(t, f"delta {name}", torch.float32, 2)
+        if tuple(t.shape) != (n, width):
+            raise KernelError(f"delta prepare: {name} {tuple(t.shape)}, expected {(n, width)}")
+    _check(lib().mll_delta_prepare(
+        _ptr(proj), _ptr(rate), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(tok_seq),
+        _ptr(seq_slot), _ptr(seq_qstart), _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), dtype_code(proj.dtype),
+        ctypes.c_int(n), ctypes.c_int(proj.shape[1]), ctypes.c_int(rate.shape[1]), ctypes.c_int(n_heads),
+        ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(taps), ctypes.c_float(unit_eps),
+        _stream()), "delta_prepare")
+
+
+def conv_state_update(proj, conv_state, seq_slot, seq_qstart, seq_qlen, n_seqs: int, channels: int, taps: int) -> None:
+    """conv_state[slot] <- the last taps - 1 rows of (conv_state[slot], this step's rows of proj[:, :channels])."""
+    _need(proj, "conv state proj", None, 2)
+    _need(conv_state, "conv state", torch.float32, 3)
+    if tuple(conv_state.shape[1:]) != (max(taps - 1, 0), channels):
+        raise KernelError(f"conv state update: state {tuple(conv_state.shape)} for {channels} channels of {taps} taps")
+    _check(lib().mll_conv_state_update(
+        _ptr(proj), dtype_code(proj.dtype), ctypes.c_int(proj.shape[1]), _ptr(conv_state), _ptr(seq_slot),
+        _ptr(seq_qstart), _ptr(seq_qlen), ctypes.c_int(n_seqs), ctypes.c_int(channels), ctypes.c_int(taps), _stream()),
+        "conv_state_update")
+
+
+def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, seq_qlen, n_seqs: int, n_heads: int,
+               n_kv_heads: int, d: int, dv: int) -> None:
+    """The recurrence S <- decay S + k u^T, o = S^T q over each sequence's tokens of the step, from and to
+    state [slots, H, d, dv] (float32).  With g [T, H * d] and beta [T, H]: the gated delta rule
+    (u = beta (v - S^T k) after the decay); else head_decay float32 [H] and u = v."""
+    n = q.shape[0]
+    delta = g is not None
+    for name, t, width in (("q", q, n_kv_heads * d), ("k", k, n_kv_heads * d), ("v", v, n_heads * dv),
+                           ("out", out, n_heads * dv)):
+        _need(t, f"state scan {name}", torch.float32, 2)
+        if tuple(t.shape) != (n, width):
+            raise KernelError(f"state scan: {name} {tuple(t.shape)}, expected {(n, width)}")
+    _need(state, "state scan state", torch.float32, 4)
+    if tuple(state.shape[1:]) != (n_heads, d, dv):
+        raise KernelError(f"state scan: state {tuple(state.shape)} for {n_heads} heads of {d} x {dv}")
+    if delta:
+        _need(g, "state scan g", torch.float32, 2)
+        _need(beta, "state scan beta", torch.float32, 2)
+        if tuple(g.shape) != (n, n_heads * d) or tuple(beta.shape) != (n, n_heads):
+            raise KernelError("state scan: g or beta of the wrong size")
+    else:
+        _need(head_decay, "state scan decay", torch.float32, 1)
+        if head_decay.shape[0] != n_heads:
+            raise KernelError("state scan: one decay per head is needed")
+    _check(lib().mll_state_scan(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(head_decay), _ptr(state), _ptr(out), _ptr(seq_slot),
+        _ptr(seq_qstart), _ptr(seq_qlen), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(int(delta)), _stream()), "state_scan")
+
+
+GATE_SILU, GATE_SIGMOID = 0, 1
+
+
+def head_norm_gate(o, weight, gate, out, n_heads: int, dv: int, eps: float, act: int, gate_col: int = 0) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]); o float32
+    [T, H * dv], weight float32 [dv] or None, gate [T, ld] of which columns gate_col .. gate_col + H * dv are read."""
+    _need(o, "head norm o", torch.float32, 2)
+    _need(gate, "head norm gate", None, 2)
+    _need(out, "head norm out", None, 2)
+    n = o.shape[0]
+    if (tuple(o.shape) != (n, n_heads * dv) or tuple(out.shape) != (n, n_heads * dv) or gate.shape[0] != n
+            or gate_col < 0 or gate_col + n_heads * dv > gate.shape[1]):
+        raise KernelError(f"head norm gate: o {tuple(o.shape)}, out {tuple(out.shape)}, gate {tuple(gate.shape)}")
+    if weight is not None:
+        _need(weight, "head norm weight", torch.float32, 1)
+        if weight.shape[0] != dv:
+            raise KernelError("head norm gate: the weight has one entry per value channel of a head")
+    _check(lib().mll_head_norm_gate(
+        _ptr(o), _ptr(weight), ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()),
+        dtype_code(gate.dtype), ctypes.c_int(gate.shape[1]), _ptr(out),
+        dtype_code(out.dtype), ctypes.c_int(n), ctypes.c_int(n_heads), ctypes.c_int(dv), ctypes.c_float(eps),
+        ctypes.c_int(act), _stream()), "head_norm_gate")

@@ -15,6 +15,7 @@ namespace mll {
 // r reads x row rows[r]; the residual add is then not written back to x.
 template <typename DeltaT, typename OutT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
+                                   const DeltaT* __restrict__ delta2,
                                    const float* __restrict__ weight, OutT* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps) {
   extern __shared__ float row_buf[];
@@ -23,11 +24,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restri
   const int src = rows ? rows[r] : r;
   float* xr = x + (size_t)src * width;
   const DeltaT* dr = delta ? delta + (size_t)src * width : nullptr;
+  const DeltaT* dr2 = delta2 ? delta2 + (size_t)src * width : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = xr[i];
     if (dr) {
-      v += to_float(dr[i]);
+      v += dr2 ? to_float(dr[i]) + to_float(dr2[i]) : to_float(dr[i]);
       if (!rows) xr[i] = v;
     }
     row_buf[i] = v;
@@ -68,6 +70,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 template <typename DeltaT, typename OutT, int NV>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
+                       const DeltaT* __restrict__ delta2,
                        const float* __restrict__ weight, OutT* __restrict__ out,
                        const int* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[32];
@@ -90,7 +93,13 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int g = threadIdx.x + k * 256;
-      if (g < groups) dl[k] = load4<DeltaT>(dr + 4 * g);
+      if (g < groups) {
+        dl[k] = load4<DeltaT>(dr + 4 * g);
+        if (delta2) {  // the outputs of two parts that read the same norm: their sum first, then the stream
+          const float4 d2 = load4<DeltaT>(delta2 + (size_t)src * width + 4 * g);
+          dl[k].x += d2.x; dl[k].y += d2.y; dl[k].z += d2.z; dl[k].w += d2.w;
+        }
+      }
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -120,21 +129,22 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
 }
 
 template <typename DeltaT, typename OutT>
-int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
-                       int n_rows, int width, float eps, cudaStream_t stream) {
+int launch_add_rmsnorm(float* x, const void* delta, const void* delta2, const float* weight, void* out,
+                       const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
   const bool aligned = width % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
-                       ((uintptr_t)out % 8 == 0) && (!delta || (uintptr_t)delta % 8 == 0);
+                       ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 8 == 0) &&
+                       (!delta2 || (uintptr_t)delta2 % 8 == 0);
   if (aligned && width <= 4 * 256 * 8) {
     const int groups = width / 4;
     if (groups <= 256 * 2)
-      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 2>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
-                 (OutT*)out, rows, width, eps);
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 2>), n_rows, 256, 0, stream, x, (const DeltaT*)delta,
+                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps);
     else if (groups <= 256 * 4)
-      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 4>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
-                 (OutT*)out, rows, width, eps);
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 4>), n_rows, 256, 0, stream, x, (const DeltaT*)delta,
+                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps);
     else
-      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 8>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
-                 (OutT*)out, rows, width, eps);
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 8>), n_rows, 256, 0, stream, x, (const DeltaT*)delta,
+                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps);
     MLL_LAUNCH_CHECK();
     return 0;
   }
@@ -148,7 +158,8 @@ int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* o
       return (int)err;
     }
   }
-  MLL_LAUNCH((kernel), n_rows, threads, smem, stream, x, (const DeltaT*)delta, weight, (OutT*)out, rows, width, eps);
+  MLL_LAUNCH((kernel), n_rows, threads, smem, stream, x, (const DeltaT*)delta, (const DeltaT*)delta2, weight,
+             (OutT*)out, rows, width, eps);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -185,21 +196,32 @@ MLL_API int mll_apply_row_norm(const void* values, const float* sumsq, int parti
   return 0;
 }
 
-// x: float32 [*, width] residual stream; delta: optional [*, width] of `act_dtype`;
-// weight: float32 [width]; out: [n_rows, width] of `act_dtype`; rows: optional int32
-// [n_rows] gather list.
-MLL_API int mll_add_rmsnorm(float* x, const void* delta, const float* weight, void* out,
-                            const int* rows, int act_dtype, int n_rows, int width, float eps,
-                            cudaStream_t stream) {
+// x: float32 [*, width] residual stream; delta, delta2: optional [*, width] of `delta_dtype` (delta2 only with
+// delta: the outputs of two parts that read the same norm); weight: float32 [width]; out: [n_rows, width] of
+// `out_dtype`; rows: optional int32 [n_rows] gather list.  out may be x itself (float32): a block reads its
+// whole row before it writes.
+MLL_API int mll_add2_rmsnorm(float* x, const void* delta, const void* delta2, const float* weight, void* out,
+                             const int* rows, int delta_dtype, int out_dtype, int n_rows, int width, float eps,
+                             cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
   MLL_REQUIRE(width <= 50 * 1024, "rmsnorm: width %d exceeds the 51200 floats one block can hold", width);
   MLL_REQUIRE(eps >= 0.f, "rmsnorm: eps must be non-negative");
+  MLL_REQUIRE(delta || !delta2, "rmsnorm: a second delta without a first");
   if (n_rows == 0) return 0;
-  if (act_dtype == MLL_F32)
-    return mll::launch_add_rmsnorm<float, float>(x, delta, weight, out, rows, n_rows, width, eps, stream);
-  if (act_dtype == MLL_BF16)
-    return mll::launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, out, rows, n_rows,
+  if (delta_dtype == MLL_F32 && out_dtype == MLL_F32)
+    return mll::launch_add_rmsnorm<float, float>(x, delta, delta2, weight, out, rows, n_rows, width, eps, stream);
+  if (delta_dtype == MLL_BF16 && out_dtype == MLL_BF16)
+    return mll::launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, delta2, weight, out, rows, n_rows,
                                                                  width, eps, stream);
-  MLL_REQUIRE(false, "rmsnorm: unknown dtype %d", act_dtype);
+  if (delta_dtype == MLL_BF16 && out_dtype == MLL_F32)
+    return mll::launch_add_rmsnorm<__nv_bfloat16, float>(x, delta, delta2, weight, out, rows, n_rows, width, eps,
+                                                         stream);
+  MLL_REQUIRE(false, "rmsnorm: dtypes %d / %d", delta_dtype, out_dtype);
   return -1;
+}
+
+MLL_API int mll_add_rmsnorm(float* x, const void* delta, const float* weight, void* out,
+                            const int* rows, int act_dtype, int n_rows, int width, float eps,
+                            cudaStream_t stream) {
+  return mll_add2_rmsnorm(x, delta, nullptr, weight, out, rows, act_dtype, act_dtype, n_rows, width, eps, stream);
 }

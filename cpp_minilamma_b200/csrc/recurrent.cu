@@ -1,0 +1,404 @@
+// Mixers that carry a matrix-valued state per sequence and head instead of keys and values:
+//
+//   S_t = diag(g_t) S_(t-1) + k_t u_t^T,      o_t = S_t^T q_t          S is [d, dv], float32
+//
+// with  u_t = v_t                              and one fixed decay per head      ("retention"), or
+//       u_t = beta_t (v_t - (diag(g_t) S_(t-1))^T k_t), g_t per key channel      (the gated delta rule).
+// The read-out sees the current token's write.  Everything that enters the recurrence is float32.
+//
+// Kernels (each for prompts and single tokens alike; a step's tokens of one sequence are consecutive rows):
+//   * retention_prepare   rotary encoding of q and k (first `rot` dimensions of a head), k / sqrt(d); q, k, v
+//                         to float32
+//   * delta_prepare       short causal convolution over time + silu on q, k, v (the inputs before this step's
+//                         first token come from the sequence's state), q and k to unit length per head,
+//                         q / sqrt(d), beta = sigmoid, g = exp(-exp(A) softplus(x + bias))
+//   * conv_state_update   the last taps - 1 convolution inputs of every sequence, kept for the next step
+//   * state_scan          the recurrence: a column of S lives in the registers of R lanes (ROWS rows each);
+//                         per token every product is local to the column, two shuffles-reductions over the
+//                         R lanes give S^T k and S^T q
+//   * head_norm_gate      o / rms(o) per head (* weight) * silu or sigmoid of a gate, to the activation dtype
+#include "common.cuh"
+
+namespace mll {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ---------------------------------------------------------------------------------------------- //
+struct RetPrepArgs {
+  const void* proj;   // [T, ld]: q (H * d), k (H * d), v (H * dv), then whatever else
+  const float* cos_table;
+  const float* sin_table;
+  const int* tok_pos;
+  float* q;           // [T, H, d]
+  float* k;
+  float* v;           // [T, H, dv]
+  int ld, n_heads, d, dv, rot, interleaved;
+  float k_scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) retention_prepare_kernel(RetPrepArgs a) {
+  const int t = blockIdx.x;
+  const int d = a.d, n = a.n_heads * d, nv = a.n_heads * a.dv;
+  const T* row = (const T*)a.proj + (size_t)t * a.ld;
+  const int pos = a.tok_pos[t];
+  const int half = a.rot >> 1;
+  const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
+  const float* sn = a.cos_table ? a.sin_table + (size_t)pos * half : nullptr;
+  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {
+    const bool is_q = i < n;
+    const int c = is_q ? i : i - n;
+    const int head = c / d, e = c % d;
+    const T* src = row + (is_q ? 0 : n) + head * d;
+    float x = to_float(src[e]);
+    if (cs && e < a.rot) {
+      int pair, partner;
+      bool first;
+      if (a.interleaved) {
+        pair = e >> 1; first = !(e & 1); partner = e ^ 1;
+      } else {
+        first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half;
+      }
+      const float y = to_float(src[partner]);
+      const float co = cs[pair], si = sn[pair];
+      x = first ? x * co - y * si : x * co + y * si;
+    }
+    if (is_q)
+      a.q[(size_t)t * n + c] = x;
+    else
+      a.k[(size_t)t * n + c] = x * a.k_scale;
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) a.v[(size_t)t * nv + i] = to_float(row[2 * n + i]);
+}
+
+// ---------------------------------------------------------------------------------------------- //
+struct DeltaPrepArgs {
+  const void* proj;        // [T, ld]: q (G * d), k (G * d), v (H * dv), beta (H)
+  const float* rate;       // [T, rate_ld]: the decay's pre-activation (H * d), float32
+  const float* conv_w;     // [C, taps], C = 2 G d + H dv, rows in the order of proj's columns
+  const float* conv_state; // [slots, taps - 1, C]
+  const float* a_log;      // [H]
+  const float* dt_bias;    // [H * d]
+  const int* tok_seq;
+  const int* seq_slot;
+  const int* seq_qstart;
+  float* q;                // [T, G, d]
+  float* k;
+  float* v;                // [T, H, dv]
+  float* g;                // [T, H, d]
+  float* beta;             // [T, H]
+  int ld, rate_ld, n_heads, n_kv_heads, d, dv, taps;
+  float unit_eps;
+};
+
+// one block per token; dynamic shared memory: C floats
+template <typename T>
+__global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepArgs a) {
+  extern __shared__ float conv_out[];
+  const int t = blockIdx.x;
+  const int H = a.n_heads, G = a.n_kv_heads, d = a.d, dv = a.dv, taps = a.taps;
+  const int nqk = G * d, C = 2 * nqk + H * dv;
+  const int seq = a.tok_seq[t];
+  const int local = t - a.seq_qstart[seq];  // index among this step's tokens of the sequence
+  const float* state = a.conv_state + (size_t)a.seq_slot[seq] * (taps - 1) * C;
+  const T* proj = (const T*)a.proj;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float y = 0.f;
+    for (int back = 0; back < taps; ++back) {  // the input `back` tokens ago meets tap taps - 1 - back
+      float x;
+      if (back <= local)
+        x = to_float(proj[(size_t)(t - back) * a.ld + c]);
+      else
+        x = state[(size_t)(local - back + taps - 1) * C + c];
+      y = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - back)], x, y);
+    }
+    conv_out[c] = silu_f(y);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  // q and k heads: unit length (and q / sqrt(d)); one warp per head
+  for (int hd = warp; hd < 2 * G; hd += n_warps) {
+    const float* x = conv_out + hd * d;
+    float ss = 0.f;
+    for (int e = lane; e < d; e += 32) ss += x[e] * x[e];
+    ss = warp_sum(ss);
+    const bool is_q = hd < G;
+    const float f = (is_q ? rsqrtf((float)d) : 1.f) / sqrtf(ss + a.unit_eps);
+    float* dst = (is_q ? a.q : a.k) + ((size_t)t * G + (is_q ? hd : hd - G)) * d;
+    for (int e = lane; e < d; e += 32) dst[e] = x[e] * f;
+  }
+  for (int i = threadIdx.x; i < H * dv; i += blockDim.x) a.v[(size_t)t * H * dv + i] = conv_out[2 * nqk + i];
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    a.beta[(size_t)t * H + i] = sigmoid_f(to_float(proj[(size_t)t * a.ld + C + i]));
+  for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+    const float sp = softplus_f(a.rate[(size_t)t * a.rate_ld + i] + a.dt_bias[i]);
+    a.g[(size_t)t * H * d + i] = expf(-expf(a.a_log[i / d]) * sp);
+  }
+}
+
+// grid (ceil(C / 128), sequences): new state = the last taps - 1 of (old state, this step's inputs)
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, float* __restrict__ conv_state,
+                                         const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                                         const int* __restrict__ seq_qlen, int C, int taps) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = blockIdx.y;
+  const int n = seq_qlen[seq], row0 = seq_qstart[seq], keep = taps - 1;
+  float* state = conv_state + (size_t)seq_slot[seq] * keep * C;
+  if (n >= keep) {
+    for (int i = 0; i < keep; ++i) state[(size_t)i * C + c] = to_float(proj[(size_t)(row0 + n - keep + i) * ld + c]);
+  } else {
+    for (int i = 0; i < keep - n; ++i) state[(size_t)i * C + c] = state[(size_t)(i + n) * C + c];  // ascending: reads run ahead of writes
+    for (int i = 0; i < n; ++i) state[(size_t)(keep - n + i) * C + c] = to_float(proj[(size_t)(row0 + i) * ld + c]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- //
+struct ScanArgs {
+  const float* q;           // [T, G, d]
+  const float* k;           // [T, G, d]
+  const float* v;           // [T, H, dv]
+  const float* g;           // [T, H, d] (DELTA) or null
+  const float* beta;        // [T, H] (DELTA) or null
+  const float* head_decay;  // [H] (not DELTA)
+  float* state;             // [slots, H, d, dv]
+  float* out;               // [T, H, dv]
+  const int* seq_slot;
+  const int* seq_qstart;
+  const int* seq_qlen;
+  int n_heads, n_kv_heads, d, dv, tok_stage;
+};
+
+constexpr int SCAN_THREADS = 128;
+
+// grid (column tiles, H, sequences).  Lane layout inside a warp: lane = r * (32 / R) + c; lane (r, c) holds rows
+// r * ROWS .. r * ROWS + ROWS - 1 of column c of the warp's columns.  Rows past d are padding: their k and q
+// are staged as 0, so their S stays 0 and adds nothing.
+template <int ROWS, int R, bool DELTA>
+__global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
+  extern __shared__ __align__(16) float stage[];
+  constexpr int DP = ROWS * R;          // padded number of rows
+  constexpr int CPW = 32 / R;           // columns per warp
+  constexpr int CPB = CPW * (SCAN_THREADS / 32);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = lane / CPW, cw = lane % CPW;
+  const int col = blockIdx.x * CPB + warp * CPW + cw;
+  const int h = blockIdx.y, seq = blockIdx.z;
+  const int H = a.n_heads, G = a.n_kv_heads, d = a.d, dv = a.dv;
+  const int kvh = h / (H / G);
+  const int row0 = a.seq_qstart[seq], n_tok = a.seq_qlen[seq];
+  const bool live = col < dv;
+  float* S = a.state + (((size_t)a.seq_slot[seq] * H + h) * d) * dv;
+  float s[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int row = r * ROWS + i;
+    s[i] = (live && row < d) ? S[(size_t)row * dv + col] : 0.f;
+  }
+  const int TS = a.tok_stage;
+  float* q_s = stage;                 // [TS][DP]
+  float* k_s = q_s + TS * DP;
+  float* g_s = k_s + TS * DP;         // DELTA only
+  const float decay = DELTA ? 1.f : a.head_decay[h];
+  for (int t0 = 0; t0 < n_tok; t0 += TS) {
+    const int nt = min(TS, n_tok - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * DP; i += SCAN_THREADS) {
+      const int tt = i / DP, e = i % DP;
+      const size_t tok = (size_t)(row0 + t0 + tt);
+      const bool in = e < d;
+      q_s[i] = in ? a.q[(tok * G + kvh) * d + e] : 0.f;
+      k_s[i] = in ? a.k[(tok * G + kvh) * d + e] : 0.f;
+      if (DELTA) g_s[i] = in ? a.g[(tok * H + h) * d + e] : 1.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const size_t tok = (size_t)(row0 + t0 + tt);
+      const float* qv = q_s + tt * DP + r * ROWS;
+      const float* kv = k_s + tt * DP + r * ROWS;
+      float u = live ? a.v[(tok * H + h) * dv + col] : 0.f;
+      if (DELTA) {
+        const float* gv = g_s + tt * DP + r * ROWS;
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+          s[i] *= gv[i];
+          part = fmaf(s[i], kv[i], part);
+        }
+#pragma unroll
+        for (int o = CPW; o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        u = a.beta[tok * H + h] * (u - part);
+      }
+      float o_part = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        s[i] = DELTA ? fmaf(kv[i], u, s[i]) : fmaf(decay, s[i], kv[i] * u);
+        o_part = fmaf(s[i], qv[i], o_part);
+      }
+#pragma unroll
+      for (int o = CPW; o < 32; o <<= 1) o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
+      if (live && r == 0) a.out[(tok * H + h) * dv + col] = o_part;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+      const int row = r * ROWS + i;
+      if (row < d) S[(size_t)row * dv + col] = s[i];
+    }
+  }
+}
+
+template <int ROWS, int R, bool DELTA>
+int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
+  ScanArgs a = args;
+  constexpr int DP = ROWS * R, CPB = (32 / R) * (SCAN_THREADS / 32);
+  a.tok_stage = DP <= 128 ? 16 : (DP <= 256 ? 8 : 4);
+  const size_t smem = (size_t)a.tok_stage * DP * (DELTA ? 3 : 2) * sizeof(float);
+  const dim3 grid((a.dv + CPB - 1) / CPB, a.n_heads, n_seqs);
+  MLL_LAUNCH((state_scan_kernel<ROWS, R, DELTA>), grid, SCAN_THREADS, smem, stream, a);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+template <bool DELTA>
+int dispatch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
+  const int d = a.d;
+  if (d <= 32) return launch_scan<8, 4, DELTA>(a, n_seqs, stream);
+  if (d <= 64) return launch_scan<16, 4, DELTA>(a, n_seqs, stream);
+  if (d <= 128) return launch_scan<32, 4, DELTA>(a, n_seqs, stream);
+  if (d <= 256) return launch_scan<32, 8, DELTA>(a, n_seqs, stream);
+  if (d <= 512) return launch_scan<32, 16, DELTA>(a, n_seqs, stream);
+  return launch_scan<32, 32, DELTA>(a, n_seqs, stream);
+}
+
+// ---------------------------------------------------------------------------------------------- //
+// grid (tokens, ceil(H / 4)), one warp per (token, head):
+//   out[t, h, :] = o / sqrt(mean(o^2) + eps) * weight * act(gate[t, h, :])      act: 0 silu, 1 sigmoid
+template <typename T, typename GateT>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight,
+                                                             const GateT* __restrict__ gate, int gate_ld,
+                                                             T* __restrict__ out, int n_heads, int dv, float eps,
+                                                             int act) {
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= n_heads) return;
+  const float* row = o + ((size_t)t * n_heads + h) * dv;
+  float ss = 0.f;
+  for (int e = lane; e < dv; e += 32) ss += row[e] * row[e];
+  ss = warp_sum(ss);
+  const float f = 1.f / sqrtf(ss / (float)dv + eps);
+  const GateT* grow = gate + (size_t)t * gate_ld + (size_t)h * dv;
+  T* dst = out + ((size_t)t * n_heads + h) * dv;
+  for (int e = lane; e < dv; e += 32) {
+    const float z = to_float(grow[e]);
+    const float gv = act == 0 ? silu_f(z) : sigmoid_f(z);
+    dst[e] = from_float<T>(row[e] * f * (weight ? weight[e] : 1.f) * gv);
+  }
+}
+
+}  // namespace mll
+
+MLL_API int mll_retention_prepare(const void* proj, const float* cos_table, const float* sin_table, const int* tok_pos,
+                                  float* q, float* k, float* v, int dtype, int n_tokens, int ld, int n_heads, int d,
+                                  int dv, int rot, int interleaved, float k_scale, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && d > 0 && dv > 0, "retention prepare: bad sizes");
+  MLL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "retention prepare: %d rotated dimensions of %d", rot, d);
+  MLL_REQUIRE(ld >= n_heads * (2 * d + dv), "retention prepare: row stride %d too short", ld);
+  if (n_tokens == 0) return 0;
+  mll::RetPrepArgs a{proj, rot > 0 ? cos_table : nullptr, sin_table, tok_pos, q, k, v, ld, n_heads, d, dv, rot,
+                     interleaved, k_scale};
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::retention_prepare_kernel<float>), n_tokens, 256, 0, stream, a);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::retention_prepare_kernel<__nv_bfloat16>), n_tokens, 256, 0, stream, a);
+  else
+    MLL_REQUIRE(false, "retention prepare: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+MLL_API int mll_delta_prepare(const void* proj, const float* rate, const float* conv_w, const float* conv_state,
+                              const float* a_log, const float* dt_bias, const int* tok_seq, const int* seq_slot,
+                              const int* seq_qstart, float* q, float* k, float* v, float* g, float* beta, int dtype,
+                              int n_tokens, int ld, int rate_ld, int n_heads, int n_kv_heads, int d, int dv, int taps,
+                              float unit_eps, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "delta prepare: bad head counts");
+  MLL_REQUIRE(d > 0 && dv > 0 && taps >= 1, "delta prepare: bad sizes");
+  const int C = 2 * n_kv_heads * d + n_heads * dv;
+  MLL_REQUIRE(ld >= C + n_heads && rate_ld >= n_heads * d, "delta prepare: row strides %d / %d too short", ld, rate_ld);
+  MLL_REQUIRE((size_t)C * sizeof(float) <= 200 * 1024, "delta prepare: %d convolution channels exceed shared memory", C);
+  if (n_tokens == 0) return 0;
+  mll::DeltaPrepArgs a{proj, rate, conv_w, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, v, g, beta,
+                       ld, rate_ld, n_heads, n_kv_heads, d, dv, taps, unit_eps};
+  const size_t smem = (size_t)C * sizeof(float);
+  if (dtype == MLL_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(mll::delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MLL_LAUNCH((mll::delta_prepare_kernel<float>), n_tokens, 256, smem, stream, a);
+  } else if (dtype == MLL_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(mll::delta_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, a);
+  } else {
+    MLL_REQUIRE(false, "delta prepare: unknown dtype %d", dtype);
+  }
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+MLL_API int mll_conv_state_update(const void* proj, int dtype, int ld, float* conv_state, const int* seq_slot,
+                                  const int* seq_qstart, const int* seq_qlen, int n_seqs, int channels, int taps,
+                                  cudaStream_t stream) {
+  MLL_REQUIRE(n_seqs >= 0 && channels > 0 && taps >= 1 && ld >= channels, "conv state update: bad sizes");
+  if (n_seqs == 0 || taps == 1) return 0;
+  MLL_REQUIRE(n_seqs <= 65535, "conv state update: too many sequences for one launch");
+  const dim3 grid((channels + 127) / 128, n_seqs);
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::conv_state_update_kernel<float>), grid, 128, 0, stream, (const float*)proj, ld, conv_state,
+               seq_slot, seq_qstart, seq_qlen, channels, taps);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::conv_state_update_kernel<__nv_bfloat16>), grid, 128, 0, stream, (const __nv_bfloat16*)proj, ld,
+               conv_state, seq_slot, seq_qstart, seq_qlen, channels, taps);
+  else
+    MLL_REQUIRE(false, "conv state update: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// delta != 0: the gated delta rule (g, beta given); else one decay per head (head_decay given).
+MLL_API int mll_state_scan(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                           const float* head_decay, float* state, float* out, const int* seq_slot,
+                           const int* seq_qstart, const int* seq_qlen, int n_seqs, int n_heads, int n_kv_heads, int d,
+                           int dv, int delta, cudaStream_t stream) {
+  MLL_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "state scan: bad head counts");
+  MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0, "state scan: head sizes %d / %d (keys at most 1024)", d, dv);
+  MLL_REQUIRE(n_heads <= 65535 && n_seqs <= 65535, "state scan: too many heads or sequences for one launch");
+  MLL_REQUIRE(delta ? (g && beta) : (head_decay != nullptr), "state scan: the decay's inputs are missing");
+  if (n_seqs == 0) return 0;
+  mll::ScanArgs a{q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, seq_qlen, n_heads, n_kv_heads, d, dv, 0};
+  return delta ? mll::dispatch_scan<true>(a, n_seqs, stream) : mll::dispatch_scan<false>(a, n_seqs, stream);
+}
+
+MLL_API int mll_head_norm_gate(const float* o, const float* weight, const void* gate, int gate_dtype, int gate_ld,
+                               void* out, int out_dtype, int n_tokens, int n_heads, int dv, float eps, int act,
+                               cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && dv > 0 && gate_ld >= n_heads * dv, "head norm gate: bad sizes");
+  MLL_REQUIRE(act == 0 || act == 1, "head norm gate: unknown activation %d", act);
+  if (n_tokens == 0) return 0;
+  const dim3 grid(n_tokens, (n_heads + 3) / 4);
+  MLL_REQUIRE(grid.y <= 65535, "head norm gate: too many heads for one launch");
+#define MLL_HNG(T, GT)                                                                                          \
+  MLL_LAUNCH((mll::head_norm_gate_kernel<T, GT>), grid, 128, 0, stream, o, weight, (const GT*)gate, gate_ld, \
+             (T*)out, n_heads, dv, eps, act)
+  if (out_dtype == MLL_F32 && gate_dtype == MLL_F32) MLL_HNG(float, float);
+  else if (out_dtype == MLL_BF16 && gate_dtype == MLL_BF16) MLL_HNG(__nv_bfloat16, __nv_bfloat16);
+  else if (out_dtype == MLL_BF16 && gate_dtype == MLL_F32) MLL_HNG(__nv_bfloat16, float);
+  else MLL_REQUIRE(false, "head norm gate: dtypes %d / %d", out_dtype, gate_dtype);
+#undef MLL_HNG
+  MLL_LAUNCH_CHECK();
+  return 0;
+}

@@ -88,7 +88,7 @@ class Model:
         for spec in self.weight_specs():
             n = 1
             for dim in spec.shape:
-                n *= dim
+                n *= max(dim, 0)  # a size that only the file gives counts as unknown
             total += n
         return total
 

@@ -38,6 +38,8 @@ class WeightSpec:
     kind: "matrix" follows the run's dtype unless the file stores it in 32-bit (then it
     stays 32-bit); "vector" (norm weights, biases) is always held as float32, which keeps
     every stored value exactly; "int_table" is held as int32.
+    A dimension of -1 is read from the file (a size that the configuration does not give); random
+    weights cannot be drawn for such a tensor.
     init: how the random-weights mode fills it: "normal" N(0, matrix_std), "norm"
     1 + N(0, norm_std), "zeros", "ones".
     """
@@ -90,11 +92,13 @@ class ModelSpec:
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values per position: pages of [n_kv_heads, PAGE, head_dim].  `window` > 0
-    means only the last `window` positions are ever read."""
+    means only the last `window` positions are ever read.  `v_head_dim` > 0: the values' head size
+    where it differs from the keys' (value pages are then [n_kv_heads, PAGE, v_head_dim])."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -137,6 +141,16 @@ class ResidualTarget:
 
     x: torch.Tensor
     norm: "Norm"
+
+
+@dataclass
+class PendingSum:
+    """The outputs of two parts that read the same norm (a block whose mixer and feed-forward run side by
+    side), both still to be added to the residual stream: the next norm adds `first + second` to it in
+    float32 in the same kernel that normalises."""
+
+    first: torch.Tensor
+    second: torch.Tensor
 
 
 # --------------------------------------------------------------------------- #
@@ -261,7 +275,8 @@ class Norm(Part):
     def forward(self, step, x: torch.Tensor, delta: Optional[torch.Tensor],
                 rows: Optional[torch.Tensor] = None, out_name: str = "h") -> torch.Tensor:
         """x += delta (in place, float32), return norm(x) in the activation dtype; with
-        `rows` only those rows, x unchanged.  A `PreNormed` made for this norm is handed on as it is."""
+        `rows` only those rows, x unchanged.  A `PreNormed` made for this norm is handed on as it is;
+        a `PendingSum` adds both of its tensors."""
         raise NotImplementedError
 
     def prenorm_weight(self):

@@ -2,6 +2,8 @@
 
 `pre_norm` is the reference's layer (src/forward.cc:385-414):
     r = x + mixer(norm_in(x));   x' = r + feed_forward(norm_post(r))
+`parallel` (not in the reference) lets mixer and feed-forward read one norm:
+    h = norm(x);   x' = x + mixer(h) + feed_forward(h)
 The residual adds are not separate kernels: a part's output stays "pending" until the
 next norm, which adds it to the float32 residual and normalises in one pass.  Where the parts on both
 sides of a norm offer it, the norm is no kernel either: the part before adds to the residual stream
@@ -11,7 +13,7 @@ from __future__ import annotations
 
 from typing import List
 
-from .base import Block, ResidualTarget, register_part
+from .base import Block, PendingSum, ResidualTarget, register_part
 
 
 def _offer(x, norm, writer, reader):
@@ -40,4 +42,22 @@ class PreNormBlock(Block):
         return layer.feed_forward.forward(step, h, into=into) if into else layer.feed_forward.forward(step, h)
 
 
+class ParallelBlock(Block):
+    """One norm, two readers:   h = norm(x);  x' = x + mixer(h) + feed_forward(h).
+    Both outputs stay pending; the next norm adds their sum to the float32 stream.  A layer without a
+    feed-forward (kind "none") leaves the mixer's output alone."""
+
+    capturable = True
+
+    def norm_names(self) -> List[str]:
+        return ["input"]
+
+    def forward(self, step, x, pending, layer, cache):
+        h = layer.norms["input"].forward(step, x, pending)
+        mixed = layer.mixer.forward(step, h, cache)
+        fed = layer.feed_forward.forward(step, h)
+        return mixed if fed is None else PendingSum(mixed, fed)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

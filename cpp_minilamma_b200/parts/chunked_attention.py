@@ -1,0 +1,114 @@
+"""Grouped-query attention whose keys and values have head sizes of their own, masked in chunks.
+
+    q = W_q h, k = W_k h, v = W_v h                       Hq heads of d, Hk heads of d, Hk heads of dv
+    q <- q / rms(q) * w_q,  k <- k / rms(k) * w_k         over the whole projection, all heads at once (optional)
+    rotate the first `rotary_dims` dimensions of every q and k head by position * f_i
+    score(i, j) = scale * q_i . k_j   for j <= i, j // chunk == i // chunk (chunk 0: every j <= i),
+                                      and j > i - window where window > 0
+    out = W_o concat_heads(softmax(score) v)
+
+Chunks count from position 0 of the sequence, not from where a step's tokens begin.  Keys and values live in
+the paged cache; a chunked layer asks the cache to keep only what its chunk can still reach (a window of one
+chunk), so pages of finished chunks go back to the pool.  Every constant is a parameter; the Llama attention
+of `parts/attention.py` is the case d == dv, scale 1 / sqrt(d), no chunk, no norm, all dimensions rotated,
+which has kernels of its own.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import BuildContext, CacheNeed, KVNeed, Mixer, WeightSpec, register_part
+from .linear import Linear
+from .rope import shared_position_encoding
+
+
+class ChunkedAttention(Mixer):
+    """params:
+      n_heads, n_kv_heads, head_dim, v_head_dim     sizes
+      scale                                         factor on q . k
+      chunk                                         0 = plain causal
+      window                                        0 = none
+      position                                      PartSpec of a rotary encoding over `rotary_dims` dimensions, or None
+      rotary_dims                                   how many leading dimensions of a head are rotated
+      qk_norm                                       None or {"q": tensor name, "k": tensor name, "eps": float}
+      names                                         {"q","k","v","o"}: tensor names
+    """
+
+    capturable = True
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.n_heads = int(params["n_heads"])
+        self.n_kv_heads = int(params["n_kv_heads"])
+        self.d = int(params["head_dim"])
+        self.dv = int(params.get("v_head_dim") or self.d)
+        self.scale = float(params["scale"])
+        self.chunk = int(params.get("chunk") or 0)
+        self.window = int(params.get("window") or 0)
+        self.names = dict(params["names"])
+        self.qk_norm = dict(params["qk_norm"]) if params.get("qk_norm") else None
+        self.rot = int(params.get("rotary_dims") or 0) if params.get("position") else 0
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
+        if self.rot % 2 or self.rot > self.d:
+            raise ValueError(f"attention: {self.rot} rotated dimensions of a head of {self.d}")
+        if self.dv > 256:
+            raise ValueError(f"attention: value heads of {self.dv} exceed the 256 the kernel takes")
+        self.position = shared_position_encoding(params["position"], ctx) if self.rot else None
+        self.qkv: Optional[Linear] = None
+        self.o: Optional[Linear] = None
+        self.q_weight = self.k_weight = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D = self.ctx.hidden_size
+        specs = [WeightSpec(self.names["q"], (self.n_heads * self.d, D)),
+                 WeightSpec(self.names["k"], (self.n_kv_heads * self.d, D)),
+                 WeightSpec(self.names["v"], (self.n_kv_heads * self.dv, D)),
+                 WeightSpec(self.names["o"], (D, self.n_heads * self.dv))]
+        if self.qk_norm:
+            specs.append(WeightSpec(self.qk_norm["q"], (self.n_heads * self.d,), kind="vector", init="norm"))
+            specs.append(WeightSpec(self.qk_norm["k"], (self.n_kv_heads * self.d,), kind="vector", init="norm"))
+        return specs
+
+    def bind(self, store) -> None:
+        mats = [store.take(self.names[p]) for p in ("q", "k", "v")]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.qkv = Linear(torch.cat(mats, dim=0), self.names["q"] + "+k+v")
+        del mats
+        self.o = Linear(store.take(self.names["o"]), self.names["o"])
+        if self.qk_norm:
+            self.q_weight = store.take(self.qk_norm["q"])
+            self.k_weight = store.take(self.qk_norm["k"])
+
+    def parameter_bytes(self) -> int:
+        return self.qkv.parameter_bytes() + self.o.parameter_bytes()
+
+    def cache_need(self) -> CacheNeed:
+        # a query reads nothing before its chunk's first key, which lies less than `chunk` positions back
+        reach = self.chunk if self.window <= 0 else (min(self.chunk, self.window) if self.chunk else self.window)
+        return CacheNeed(kv=KVNeed(self.n_kv_heads, self.d, reach, self.dv if self.dv != self.d else 0))
+
+    def forward(self, step, h, cache):
+        T = h.shape[0]
+        act = self.ctx.act_dtype
+        if cache.k is None:
+            raise RuntimeError("attention: the cache view has no key/value storage")
+        qkv = self.qkv.forward(step, h, "qkv")
+        cos, sin = self.position.tables() if self.position is not None else (None, None)
+        q = step.ws.buffer("q", (T, self.n_heads * self.d), act)
+        K.local_attention_prepare(qkv, self.q_weight, self.k_weight, cos, sin, step.tok_pos, step.tok_seq,
+                                  step.seq_slot, cache.block_table, q, cache.k, cache.v, self.n_heads,
+                                  self.n_kv_heads, self.d, self.dv, self.rot,
+                                  bool(self.position.interleaved) if self.position is not None else False,
+                                  float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
+        out = step.ws.buffer("attn", (T, self.n_heads * self.dv), act)
+        K.local_attention(q, cache.k, cache.v, step.tok_pos, step.tok_seq, step.seq_slot, cache.block_table, out,
+                          self.n_heads, self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale)
+        return self.o.forward(step, out, "o")
+
+
+register_part("mixer", "chunked_attention", ChunkedAttention)

@@ -12,12 +12,13 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import BuildContext, Part, WeightSpec, register_part
+from .base import BuildContext, Part, WeightSpec, build_part, register_part
 from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    """params: vocab, name."""
+    """params: vocab, name; optional `norm`: PartSpec of a norm applied to the looked-up rows (on the
+    float32 stream itself) before the first layer."""
 
     capturable = True
 
@@ -28,16 +29,22 @@ class TokenEmbedding(Part):
         self.vocab = int(params["vocab"])
         self.name = params["name"]
         self.table: Optional[torch.Tensor] = None
+        self.norm = build_part("norm", params["norm"], ctx) if params.get("norm") else None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name, (self.vocab, self.ctx.hidden_size))]
+        specs = [WeightSpec(self.name, (self.vocab, self.ctx.hidden_size))]
+        return specs + (self.norm.weight_specs() if self.norm is not None else [])
 
     def bind(self, store) -> None:
         self.table = store.get(self.name)  # left in the store: a tied head takes it too
+        if self.norm is not None:
+            self.norm.bind(store)
 
     def forward(self, step, tokens: torch.Tensor) -> torch.Tensor:
         x = step.ws.buffer("x", (tokens.shape[0], self.ctx.hidden_size), torch.float32)
         K.embedding(tokens, self.table, x)
+        if self.norm is not None:
+            self.norm.forward_in_place(x)
         return x
 
 

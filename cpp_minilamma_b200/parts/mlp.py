@@ -33,7 +33,8 @@ def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor):
 
 
 class SwiGLUFeedForward(FeedForward):
-    """params: intermediate, names {"gate","up","down"} (tensor name stems)."""
+    """params: intermediate, names {"gate","up","down"} (tensor name stems, ".weight" is appended; with
+    `bare_names` they are the tensor names themselves)."""
 
     capturable = True
     takes_prenormed = True  # the gate/up product may read rows whose norm it finishes itself
@@ -42,22 +43,22 @@ class SwiGLUFeedForward(FeedForward):
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
         self.inter = int(params["intermediate"])
-        self.names = dict(params["names"])
+        suffix = "" if params.get("bare_names") else ".weight"
+        self.names = {k: v + suffix for k, v in dict(params["names"]).items()}
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
         self.block = 0
 
     def weight_specs(self) -> List[WeightSpec]:
         D = self.ctx.hidden_size
-        return [WeightSpec(self.names["gate"] + ".weight", (self.inter, D)),
-                WeightSpec(self.names["up"] + ".weight", (self.inter, D)),
-                WeightSpec(self.names["down"] + ".weight", (D, self.inter))]
+        return [WeightSpec(self.names["gate"], (self.inter, D)),
+                WeightSpec(self.names["up"], (self.inter, D)),
+                WeightSpec(self.names["down"], (D, self.inter))]
 
     def bind(self, store) -> None:
-        fused, self.block = fuse_gate_up(store.take(self.names["gate"] + ".weight"),
-                                         store.take(self.names["up"] + ".weight"))
+        fused, self.block = fuse_gate_up(store.take(self.names["gate"]), store.take(self.names["up"]))
         self.gate_up = Linear(fused, self.names["gate"] + "+up")
-        self.down = Linear(store.take(self.names["down"] + ".weight"), self.names["down"])
+        self.down = Linear(store.take(self.names["down"]), self.names["down"])
 
     def parameter_bytes(self) -> int:
         return self.gate_up.parameter_bytes() + self.down.parameter_bytes()
@@ -87,4 +88,14 @@ class SwiGLUFeedForward(FeedForward):
         return self.down.forward(step, act, "down", into=into)
 
 
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: contributes nothing (blocks that add two outputs skip a None)."""
+
+    capturable = True
+
+    def forward(self, step, h, into=None):
+        return None
+
+
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+register_part("feed_forward", "none", NoFeedForward)

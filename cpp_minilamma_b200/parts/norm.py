@@ -11,7 +11,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import BuildContext, Norm, PreNormed, WeightSpec, register_part
+from .base import BuildContext, Norm, PendingSum, PreNormed, WeightSpec, register_part
 
 
 class RMSNorm(Norm):
@@ -45,8 +45,15 @@ class RMSNorm(Norm):
             return delta  # x is up to date; the product that reads the rows applies the factor
         n = x.shape[0] if rows is None else rows.shape[0]
         out = step.ws.buffer(out_name, (n, self.width), self.ctx.act_dtype)
-        K.add_rmsnorm(x, delta, self.weight, out, self.eps, rows)
+        if isinstance(delta, PendingSum):
+            K.add_rmsnorm(x, delta.first, self.weight, out, self.eps, rows, delta2=delta.second)
+        else:
+            K.add_rmsnorm(x, delta, self.weight, out, self.eps, rows)
         return out
+
+    def forward_in_place(self, x) -> None:
+        """x <- norm(x) on the float32 stream itself (a norm that sits on the stream, not beside it)."""
+        K.add_rmsnorm(x, None, self.weight, x, self.eps)
 
 
 register_part("norm", "rms_norm", RMSNorm)

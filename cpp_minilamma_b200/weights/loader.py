@@ -53,7 +53,7 @@ def check_tensors(found: Dict[str, tuple], specs: Sequence[WeightSpec]) -> None:
         if name not in found:
             continue
         dtype, shape = found[name]
-        if tuple(shape) != tuple(spec.shape):
+        if len(shape) != len(spec.shape) or any(w != -1 and w != f for w, f in zip(spec.shape, shape)):
             wrong.append(f"{name}: shape {tuple(shape)}, expected {tuple(spec.shape)}")
         elif spec.kind == "int_table" and dtype not in _INTS:
             wrong.append(f"{name}: dtype {dtype}, expected an integer table")

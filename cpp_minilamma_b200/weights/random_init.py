@@ -24,6 +24,9 @@ def _fill(spec: WeightSpec, index: int, seed: int, matrix_std: float, norm_std: 
     gen = torch.Generator(device=device)
     gen.manual_seed((int(seed) * 1000003 + index * 7919 + 12345) % (2 ** 63 - 1))
     shape = tuple(spec.shape)
+    if any(dim < 0 for dim in shape):
+        raise ValueError(f"tensor {spec.name}: a size that only a file gives ({shape}); the configuration must name it "
+                         "before random weights can be drawn")
     if spec.init == "zeros":
         return torch.zeros(shape, dtype=torch.float32, device=device)
     if spec.init == "ones":
