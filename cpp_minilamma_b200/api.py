@@ -136,6 +136,13 @@ class LLM:
         return self.engine.step(entries)
 
 
+def _positions_for(max_tokens: int, max_positions: Optional[int]) -> int:
+    """Positions to build tables for when the caller names none: no sequence can grow beyond the cache's whole
+    budget (rounded up to pages), so tables past it would never be read.  The model's own limit still applies."""
+    from .cache.paged import PAGE
+    return max_positions if max_positions is not None else -(-max(int(max_tokens), 1) // PAGE) * PAGE
+
+
 def build_model(config: ModelConfig, dtype, device, max_positions: Optional[int] = None) -> Model:
     _, builder = lookup_architecture(config.architecture)
     return Model(builder(config), parse_dtype(dtype), device, max_positions)
@@ -147,7 +154,7 @@ def load(folder, dtype="bfloat16", device="cuda:0", max_tokens: int = 16384, max
     `architectures` in config.json."""
     device = require_cuda(device)
     config = load_config(folder)
-    model = build_model(config, dtype, device, max_positions)
+    model = build_model(config, dtype, device, _positions_for(max_tokens, max_positions))
     model.bind(load_tensors(Path(folder), model.weight_specs(), parse_dtype(dtype), device))
     return LLM(config, model, max_tokens, max_seqs, max_step_tokens)
 
@@ -161,7 +168,7 @@ def random_model(config: ModelConfig, seed: int = 0, dtype="bfloat16", device="c
     device = require_cuda(device)
     run_dtype = parse_dtype(dtype)
     stored = parse_dtype(stored_as) if stored_as is not None else run_dtype
-    model = build_model(config, run_dtype, device, max_positions)
+    model = build_model(config, run_dtype, device, _positions_for(max_tokens, max_positions))
     tensors = {}
     specs = model.weight_specs()
     for index, spec in enumerate(specs):  # one at a time: the float32 draft of a tensor is freed before the next

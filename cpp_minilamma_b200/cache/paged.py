@@ -190,7 +190,12 @@ class SequenceCache:
             raise CacheError("max_tokens must be positive")
         self.n_pages = (max_tokens + PAGE - 1) // PAGE
         self.n_slots = max(1, min(n_slots, self.n_pages))
-        self.max_blocks = max(1, min(self.n_pages, (max_positions + PAGE - 1) // PAGE))
+        # A sequence never holds more pages than the pool has - unless every group hands pages back behind a
+        # window: then its block table must reach as far as the positions do.
+        kv_needs = [need.kv for _, cache_of, need in needs if cache_of is None and need.kv is not None]
+        windowed = bool(kv_needs) and all(kv.window > 0 for kv in kv_needs)
+        by_positions = (max_positions + PAGE - 1) // PAGE
+        self.max_blocks = max(1, by_positions if windowed else min(self.n_pages, by_positions))
         self.max_positions = max_positions
         self.device = device
         self.dtype = dtype

@@ -146,7 +146,7 @@ class KupiraxConfig(ModelConfig):
     loop_start: int = 0
     loop_stop: int = 0
     loop_times: int = 1
-    max_positions: int = 1 << 16   # not part of the design: how many positions the rotary tables hold by default
+    max_positions: int = 1 << 20   # not part of the design: the most positions a sequence may have (tables are built for what the cache holds)
     torch_dtype: str = "bfloat16"  # storage of a folder written from this configuration
 
     @classmethod

@@ -166,3 +166,22 @@ def test_random_traffic_keeps_invariants():
         cache.release(s)
     cache.check()
     assert cache.n_free_slots == 5 and cache.free_pages() == 12
+
+
+def test_values_with_a_head_size_of_their_own_and_a_sequence_longer_than_the_pool():
+    """Keys of 16 and values of 24 per head; every group windowed, so a sequence may pass through more pages
+    than the pool has: the block table reaches as far as the positions do and old pages come back."""
+    from cpp_minilamma_b200.parts.base import CacheNeed, KVNeed
+    needs = [(0, None, CacheNeed(kv=KVNeed(2, 16, window=PAGE, v_head_dim=24)))]
+    cache = SequenceCache(needs, PAGE * 3, 2, PAGE * 10, torch.float32, "cpu")
+    view = cache.view(0)
+    assert view.k.shape[-1] == 16 and view.v.shape[-1] == 24 and view.window == PAGE
+    assert cache.max_blocks == 10
+    slot = cache.acquire(1)[0]
+    for _ in range(9):
+        cache.reserve([(slot, PAGE)])
+        cache.check()
+    assert cache.seq_len[slot] == 9 * PAGE and cache.groups[0].pool.n_free >= 1
+    cache.release(slot)
+    cache.check()
+    assert cache.groups[0].pool.n_free == 3
