@@ -1,0 +1,261 @@
+// Prompt steps of the chunked attention (attention_local.cu) on tensor cores, bfloat16: the flash-style
+// mma.sync kernel of attention_mma_prefill.cu with head sizes of their own for keys (d) and values (dv),
+// an explicit scale, and the chunk mask (key j visible from query i iff j <= i and j / chunk == i / chunk).
+// The kernel is instantiated for padded sizes DK, DV in {32, 64, 128, 256}; the real d and dv (multiples of
+// 8, so that rows are whole 16-byte words) are runtime values and the padding columns are zero-filled in
+// shared memory.  A tile starts at the first page that its first row's chunk (or window) reaches.
+#include "attention_decode.cuh"
+#include "common.cuh"
+
+namespace mll {
+
+struct LocalMmaArgs {
+  const __nv_bfloat16* q;        // [T, Hq * d]
+  const __nv_bfloat16* k_cache;  // [n_pages, Hk, PAGE, d]
+  const __nv_bfloat16* v_cache;  // [n_pages, Hk, PAGE, dv]
+  const int* seq_slot;
+  const int* seq_ctx;
+  const int* seq_qstart;
+  const int* seq_qlen;
+  const int* tile_seq;
+  const int* tile_row0;
+  const int* block_table;
+  __nv_bfloat16* out;            // [T, Hq * dv]
+  int n_heads, n_kv_heads, max_blocks, window, chunk, d, dv;
+  float scale_log2;
+};
+
+template <int DK, int DV>
+struct LocalMmaSmem {
+  static constexpr int KS = DK + 8, VS = DV + 8;
+  static constexpr int KTILE = 64 * KS, VTILE = 64 * VS;
+  static constexpr size_t BYTES = (size_t)2 * (KTILE + VTILE) * 2;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) {
+  using L = LocalMmaSmem<DK, DV>;
+  constexpr int KSTEPS = DK / 16;
+  constexpr int NT_OUT = DV / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2 stages][K 64 x KS, V 64 x VS]
+  __nv_bfloat16* q_s = kv_s + (L::KTILE + L::VTILE);                 // the query tile passes through stage 1's K tile
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int seq = a.tile_seq[blockIdx.x], row0 = a.tile_row0[blockIdx.x];
+  const int h = blockIdx.y;
+  const int kvh = h / (a.n_heads / a.n_kv_heads);
+  const int ctx = a.seq_ctx[seq], qlen = a.seq_qlen[seq];
+  const int rows = min(64, qlen - row0);
+  const int pos0 = ctx - qlen + row0;
+  const int d = a.d, dv = a.dv;
+  const int* table = a.block_table + (size_t)a.seq_slot[seq] * a.max_blocks;
+  constexpr int KCPR = DK / 8, VCPR = DV / 8;  // 16-byte words per padded row
+
+  {
+    const __nv_bfloat16* qg = a.q + ((size_t)a.seq_qstart[seq] + row0) * a.n_heads * d + (size_t)h * d;
+    for (int c = tid; c < 64 * KCPR; c += 128) {
+      const int r = c / KCPR, cc = c % KCPR;
+      const bool in = r < rows && cc * 8 < d;
+      cp_async16_zfill(q_s + r * L::KS + cc * 8, qg + (size_t)min(r, rows - 1) * a.n_heads * d + (in ? cc * 8 : 0), in);
+    }
+  }
+  auto load_page = [&](int page_index, int stage) {
+    const int page = table[page_index];
+    const __nv_bfloat16* kg = a.k_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * d;
+    const __nv_bfloat16* vg = a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * dv;
+    __nv_bfloat16* kd = kv_s + (size_t)stage * (L::KTILE + L::VTILE);
+    __nv_bfloat16* vd = kd + L::KTILE;
+    const int valid_rows = ctx - page_index * MLL_PAGE;  // rows past the cached length hold no data
+    for (int c = tid; c < MLL_PAGE * KCPR; c += 128) {
+      const int r = c / KCPR, cc = c % KCPR;
+      const bool in = cc * 8 < d && r < valid_rows;
+      cp_async16_zfill(kd + r * L::KS + cc * 8, kg + (size_t)r * d + (in ? cc * 8 : 0), in);
+    }
+    for (int c = tid; c < MLL_PAGE * VCPR; c += 128) {
+      const int r = c / VCPR, cc = c % VCPR;
+      const bool in = cc * 8 < dv && r < valid_rows;
+      cp_async16_zfill(vd + r * L::VS + cc * 8, vg + (size_t)r * dv + (in ? cc * 8 : 0), in);
+    }
+  };
+
+  int first_key = a.chunk > 0 ? (pos0 / a.chunk) * a.chunk : 0;  // of the tile's first row; later rows reach no further back
+  if (a.window > 0) first_key = max(first_key, pos0 - a.window + 1);
+  const int last_pos = pos0 + rows - 1;
+  const int last_chunk_start = a.chunk > 0 ? (last_pos / a.chunk) * a.chunk : 0;
+  const int p_first = first_key / MLL_PAGE, p_last = last_pos / MLL_PAGE;
+  load_page(p_first, 0);
+  cp_async_commit();
+
+  unsigned qf[KSTEPS][4];
+  float o[NT_OUT][4];
+#pragma unroll
+  for (int n = 0; n < NT_OUT; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int p = p_first; p <= p_last; ++p) {
+    const int stage = (p - p_first) & 1;
+    cp_async_wait<0>();
+    __syncthreads();
+    if (p == p_first) {
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks)
+        ldmatrix_x4(qf[ks], q_s + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * L::KS + ks * 16 +
+                                ((lane >> 4) << 3));
+      __syncthreads();
+    }
+    if (p < p_last) load_page(p + 1, stage ^ 1);
+    cp_async_commit();
+    const __nv_bfloat16* kt = kv_s + (size_t)stage * (L::KTILE + L::VTILE);
+    const __nv_bfloat16* vt = kt + L::KTILE;
+
+    float s_acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+      for (int n = 0; n < 8; n += 2) {
+        unsigned kb[4];
+        const int key = n * 8 + (lane & 7) + ((lane >> 4) << 3);
+        const int dim = ks * 16 + (((lane >> 3) & 1) << 3);
+        ldmatrix_x4(kb, kt + key * L::KS + dim);
+        mma_16816(s_acc[n], qf[ks], kb[0], kb[1]);
+        mma_16816(s_acc[n + 1], qf[ks], kb[2], kb[3]);
+      }
+    }
+    // mask where the page meets the diagonal, a chunk's or the window's edge, or the tile's end
+    const bool needs_mask = (p * MLL_PAGE + MLL_PAGE - 1 > pos0 + warp * 16) || a.window > 0 || rows < 64 ||
+                            p * MLL_PAGE < last_chunk_start;
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = s_acc[n][i] * a.scale_log2;
+        if (needs_mask) {
+          const int row = warp * 16 + g + ((i >> 1) << 3);
+          const int qpos = pos0 + row;
+          const int kpos = p * MLL_PAGE + n * 8 + 2 * t + (i & 1);
+          const bool ok = row < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window) &&
+                          (a.chunk <= 0 || kpos >= (qpos / a.chunk) * a.chunk);
+          v = ok ? v : -INFINITY;
+        }
+        s_acc[n][i] = v;
+      }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) mx = fmaxf(mx, fmaxf(s_acc[n][2 * r], s_acc[n][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);
+      const float base = m_new > -INFINITY ? m_new : 0.f;  // a row with nothing visible yet stays at zero weight
+      alpha[r] = exp2f(m_run[r] - base);
+      float sum = 0.f;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const float p0 = exp2f(s_acc[n][2 * r] - base), p1 = exp2f(s_acc[n][2 * r + 1] - base);
+        s_acc[n][2 * r] = p0;
+        s_acc[n][2 * r + 1] = p1;
+        sum += p0 + p1;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[r] = l_run[r] * alpha[r] + sum;
+      m_run[r] = m_new;
+    }
+#pragma unroll
+    for (int n = 0; n < NT_OUT; ++n) {
+      o[n][0] *= alpha[0];
+      o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1];
+      o[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      unsigned pa[4];
+      pa[0] = pack_bf162(s_acc[2 * ks][0], s_acc[2 * ks][1]);
+      pa[1] = pack_bf162(s_acc[2 * ks][2], s_acc[2 * ks][3]);
+      pa[2] = pack_bf162(s_acc[2 * ks + 1][0], s_acc[2 * ks + 1][1]);
+      pa[3] = pack_bf162(s_acc[2 * ks + 1][2], s_acc[2 * ks + 1][3]);
+#pragma unroll
+      for (int n = 0; n < NT_OUT; n += 2) {
+        unsigned vb[4];
+        const int key = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int col = (n + (lane >> 4)) * 8;
+        ldmatrix_x4_trans(vb, vt + key * L::VS + col);
+        mma_16816(o[n], pa, vb[0], vb[1]);
+        mma_16816(o[n + 1], pa, vb[2], vb[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + g + 8 * r;
+    if (row >= rows) continue;
+    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    __nv_bfloat16* dst = a.out + ((size_t)a.seq_qstart[seq] + row0 + row) * a.n_heads * dv + (size_t)h * dv;
+#pragma unroll
+    for (int n = 0; n < NT_OUT; ++n)
+      if (n * 8 + 2 * t < dv)  // dv is even: a pair is inside or outside as a whole
+        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + 2 * t) =
+            __floats2bfloat162_rn(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+  }
+}
+
+template <int DK, int DV>
+int launch_local_mma(const LocalMmaArgs& a, int n_tiles, cudaStream_t stream) {
+  const size_t smem = LocalMmaSmem<DK, DV>::BYTES;
+  auto kernel = local_prefill_mma_kernel<DK, DV>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) {
+    mll_set_error("local attention (mma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    return (int)err;
+  }
+  MLL_LAUNCH((kernel), dim3(n_tiles, a.n_heads), 128, smem, stream, a);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int DK>
+int dispatch_local_mma_v(const LocalMmaArgs& a, int n_tiles, cudaStream_t stream) {
+  if (a.dv <= 32) return launch_local_mma<DK, 32>(a, n_tiles, stream);
+  if (a.dv <= 64) return launch_local_mma<DK, 64>(a, n_tiles, stream);
+  if (a.dv <= 128) return launch_local_mma<DK, 128>(a, n_tiles, stream);
+  return launch_local_mma<DK, 256>(a, n_tiles, stream);
+}
+
+}  // namespace mll
+
+MLL_API int mll_local_attention_mma_supported(int dtype, int d, int dv) {
+  return dtype == MLL_BF16 && d >= 8 && d <= 256 && d % 8 == 0 && dv >= 8 && dv <= 256 && dv % 8 == 0;
+}
+
+// tile_seq / tile_row0: tiles of up to 64 query rows as (sequence, first row among the sequence's new tokens).
+MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
+                                    const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
+                                    const int* tile_row0, const int* block_table, void* out, int n_tiles, int n_heads,
+                                    int n_kv_heads, int d, int dv, int chunk, int window, int max_blocks, float scale,
+                                    cudaStream_t stream) {
+  MLL_REQUIRE(mll_local_attention_mma_supported(MLL_BF16, d, dv), "local attention (mma): head sizes %d / %d", d, dv);
+  MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention (mma): bad head counts");
+  MLL_REQUIRE(n_tiles >= 0 && n_heads <= 65535 && chunk >= 0 && window >= 0, "local attention (mma): bad tile count, chunk or window");
+  if (n_tiles == 0) return 0;
+  mll::LocalMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                      seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
+                      (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, d, dv,
+                      scale * 1.4426950408889634f};
+  if (d <= 32) return mll::dispatch_local_mma_v<32>(a, n_tiles, stream);
+  if (d <= 64) return mll::dispatch_local_mma_v<64>(a, n_tiles, stream);
+  if (d <= 128) return mll::dispatch_local_mma_v<128>(a, n_tiles, stream);
+  return mll::dispatch_local_mma_v<256>(a, n_tiles, stream);
+}

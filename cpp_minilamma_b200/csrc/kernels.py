@@ -840,6 +840,40 @@ def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table
         ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), _stream()), "local_attention")
 
 
+USE_TENSOR_CORE_LOCAL = True  # tests switch it off to reach the general kernel in bfloat16 prompt steps
+
+
+def local_attention_mma_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
+    return USE_TENSOR_CORE_LOCAL and dtype == torch.bfloat16 and bool(
+        lib().mll_local_attention_mma_supported(dtype_code(dtype), d, dv))
+
+
+def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
+                          block_table, out, n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int,
+                          scale: float) -> None:
+    """`local_attention` for prompt steps in bfloat16 on tensor cores: the work is a list of tiles of up to
+    PREFILL_TILE query rows, (sequence, first row among the sequence's new tokens)."""
+    _need(q, "local attention q", torch.bfloat16, 2)
+    _need(out, "local attention out", torch.bfloat16, 2)
+    _need(k_cache, "local attention k cache", torch.bfloat16, 4)
+    _need(v_cache, "local attention v cache", torch.bfloat16, 4)
+    n = q.shape[0]
+    if tuple(q.shape) != (n, n_heads * d) or tuple(out.shape) != (n, n_heads * dv):
+        raise KernelError(f"local attention: q {tuple(q.shape)} / out {tuple(out.shape)} for {n_heads} heads of {d} / {dv}")
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, d) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, dv):
+        raise KernelError("local attention: the caches do not fit the head sizes")
+    for name, t in (("tile_seq", tile_seq), ("tile_row0", tile_row0)):
+        _need(t, f"local attention {name}", torch.int32, 1)
+    if tile_seq.shape != tile_row0.shape:
+        raise KernelError("local attention: the tile lists differ in length")
+    _check(lib().mll_local_attention_mma(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx), _ptr(seq_qstart), _ptr(seq_qlen),
+        _ptr(tile_seq), _ptr(tile_row0), _ptr(block_table), _ptr(out), ctypes.c_int(tile_seq.shape[0]),
+        ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
+        ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), _stream()),
+        "local_attention_mma")
+
+
 # --------------------------------------------------------------------------- #
 # mixers with a matrix-valued state per sequence and head
 # --------------------------------------------------------------------------- #

@@ -92,6 +92,25 @@ class ChunkedAttention(Mixer):
         reach = self.chunk if self.window <= 0 else (min(self.chunk, self.window) if self.chunk else self.window)
         return CacheNeed(kv=KVNeed(self.n_kv_heads, self.d, reach, self.dv if self.dv != self.d else 0))
 
+    def _tensor_cores(self) -> bool:
+        return K.local_attention_mma_supported(self.ctx.act_dtype, self.d, self.dv)
+
+    def step_metadata_key(self):
+        # prompt steps on tensor cores read a list of query tiles; layers share it whatever their sizes
+        return ("chunked_attention.tiles", K.PREFILL_TILE) if self.ctx.act_dtype == torch.bfloat16 else None
+
+    def prepare_step(self, shape):
+        """Tiles of up to PREFILL_TILE query rows as (sequence, first row among the sequence's new tokens), the
+        sequences with the most rows first.  Steps of single tokens need no list."""
+        if shape.all_decode:
+            return {}
+        lists = {"tile_seq": [], "tile_row0": []}
+        for i in sorted(range(shape.n_seqs), key=lambda i: -shape.lens[i]):
+            for row0 in range(0, shape.lens[i], K.PREFILL_TILE):
+                lists["tile_seq"].append(i)
+                lists["tile_row0"].append(row0)
+        return lists
+
     def forward(self, step, h, cache):
         T = h.shape[0]
         act = self.ctx.act_dtype
@@ -106,6 +125,12 @@ class ChunkedAttention(Mixer):
                                   bool(self.position.interleaved) if self.position is not None else False,
                                   float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
         out = step.ws.buffer("attn", (T, self.n_heads * self.dv), act)
+        tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
+        if tiles and self._tensor_cores():
+            K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
+                                    tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out, self.n_heads,
+                                    self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale)
+            return self.o.forward(step, out, "o")
         K.local_attention(q, cache.k, cache.v, step.tok_pos, step.tok_seq, step.seq_slot, cache.block_table, out,
                           self.n_heads, self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale)
         return self.o.forward(step, out, "o")

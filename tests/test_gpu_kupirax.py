@@ -229,3 +229,46 @@ def test_trace_replay_writes_the_wanted_logits(models, tmp_path):
     for n, rows in want.items():
         got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(rows), -1)
         close(got, np.stack(rows), "float32", f"trace step {n}")
+
+
+@pytest.mark.parametrize("d,dv,chunk,window", [(64, 80, 64, 0), (72, 136, 48, 0), (40, 8, 0, 0), (128, 128, 200, 0),
+                                               (16, 256, 7, 0), (256, 32, 0, 50), (32, 32, 100, 30)])
+def test_tensor_core_prompt_kernel_against_the_general_one(d, dv, chunk, window):
+    """The mma.sync prompt kernel and the one-warp-per-row kernel on the same bfloat16 cache: three sequences
+    that start at positions 0, 70 and 129 (so tiles begin inside chunks and pages), pages in shuffled order."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(d * 1000 + dv)
+    H, G, n_pages = 4, 2, 16
+    starts, lens = [0, 70, 129], [150, 61, 1]
+    k_cache = (torch.randn((n_pages, G, PAGE, d), generator=gen) * 0.5).to(torch.bfloat16).to(dev)
+    v_cache = torch.randn((n_pages, G, PAGE, dv), generator=gen).to(torch.bfloat16).to(dev)
+    order = torch.randperm(n_pages, generator=gen).tolist()
+    table = torch.full((3, 8), -1, dtype=torch.int32)
+    at = 0
+    for s, (start, n) in enumerate(zip(starts, lens)):
+        blocks = -(-(start + n) // PAGE)
+        table[s, :blocks] = torch.tensor(order[at:at + blocks], dtype=torch.int32)
+        at += blocks
+    table = table.to(dev)
+    T = sum(lens)
+    q = torch.randn((T, H * d), generator=gen).to(torch.bfloat16).to(dev)
+    tile_seq, tile_row0 = [], []
+    for s, n in enumerate(lens):
+        for row0 in range(0, n, K.PREFILL_TILE):
+            tile_seq.append(s)
+            tile_row0.append(row0)
+    state = make_step_state(dev, [0, 1, 2], starts, lens)
+    tiles = torch.tensor([tile_seq, tile_row0], dtype=torch.int32, device=dev)
+    fast = torch.zeros((T, H * dv), dtype=torch.bfloat16, device=dev)
+    plain = torch.zeros_like(fast)
+    scale = 1.0 / d ** 0.5
+    K.local_attention_tiles(q, k_cache, v_cache, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
+                            tiles[0].contiguous(), tiles[1].contiguous(), table, fast, H, G, d, dv, chunk, window, scale)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, plain, H, G, d, dv,
+                      chunk, window, scale)
+    torch.cuda.synchronize()
+    err = (fast.float() - plain.float()).abs()
+    assert torch.isfinite(fast.float()).all()
+    assert err.max().item() <= 0.03 * plain.float().abs().max().item(), (err.max().item(), int(err.argmax()) // (H * dv))
