@@ -397,6 +397,165 @@ def profile_region(args):
     return 0
 
 
+# --------------------------------------------------------------------------------------------------- #
+# --design kupirax: the Kupirax decoder beside the Llama decoder at equal sizes                         #
+# --------------------------------------------------------------------------------------------------- #
+DESIGN_SIZES = {
+    # width, feed-forward and attention heads of the Llama-3.2-1B-like and Llama-3.1-8B-like layers; a group of
+    # (chunked attention, retention, gated delta rule) layers, twice; vocabulary 32,000
+    "w2048": dict(width=2048, ff=8192, vocab=32000, heads=16, kv_heads=4, chunk=1024, ret_heads=8, groups=2),
+    "w4096": dict(width=4096, ff=14336, vocab=32000, heads=32, kv_heads=8, chunk=2048, ret_heads=16, groups=2),
+}
+
+
+def kupirax_config(size):
+    import cpp_minilamma_b200 as ml
+    s = DESIGN_SIZES[size]
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    group = [
+        {"type": "attention", "mlp": mlp,
+         "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                   "mask": {"size": s["chunk"]},
+                   "rot": {"base": 500000.0, "dims": 64,
+                           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}},
+        {"type": "retention", "mlp": mlp,
+         "mixer": {"heads": s["ret_heads"], "dim": 128, "vdim": 256, "rot": {"base": 10000.0, "dims": 128},
+                   "decay": [1.0 - 2.0 ** (-5 - 4 * i / s["ret_heads"]) for i in range(s["ret_heads"])]}},
+        {"type": "channel_delta", "mlp": mlp,
+         "mixer": {"heads": s["heads"], "kv_heads": s["heads"], "dim": 128, "vdim": 128, "conv": 4,
+                   "decay_rank": 64, "gate_rank": 64}},
+    ]
+    return ml.config_from_dict({"architecture": "Kupirax", "vocab": s["vocab"], "width": s["width"],
+                                "norm": {"eps": 1e-6}, "layers": group * s["groups"], "torch_dtype": "bfloat16"})
+
+
+def llama_like_config(size):
+    import cpp_minilamma_b200 as ml
+    s = DESIGN_SIZES[size]
+    return ml.config_from_dict({
+        "architectures": ["LlamaForCausalLM"], "torch_dtype": "bfloat16", "vocab_size": s["vocab"],
+        "hidden_size": s["width"], "intermediate_size": s["ff"], "num_hidden_layers": 3 * s["groups"],
+        "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": 128,
+        "max_position_embeddings": 8192, "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-6,
+        "tie_word_embeddings": False})
+
+
+def kernel_times_of_a_step(llm, entries_of, launches=3):
+    """Device time of every kernel of this library in one eager step (CUDA events around each launch), after two
+    warm-up steps of the same kind: {kernel: (calls, ms)}."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    import torch
+    for _ in range(2):
+        slots, entries = entries_of()
+        llm.engine.step_borrowed(entries)
+        for slot in slots:
+            llm.engine.release(slot)
+    slots, entries = entries_of()
+    torch.cuda.synchronize()
+    with K.KernelTimes() as times:
+        llm.engine.step_borrowed(entries)
+    totals = times.totals()
+    for slot in slots:
+        llm.engine.release(slot)
+    return totals
+
+
+def design_rooflines(size, tokens, batch, context, peaks):
+    """Algorithmic bytes (or FLOPs) per launch of the kernels that differ between the two decoders, at the sizes of
+    `kernel_times_of_a_step`: {(model, kind of step, kernel): ("hbm" | "tensor", amount)}."""
+    s = DESIGN_SIZES[size]
+    H, G, d, dv, C = s["heads"], s["kv_heads"], 128, 128, s["chunk"]
+    Hr, dr, dvr = s["ret_heads"], 128, 256
+    out = {}
+    seen = sum(min(i % C, i) + 1 for i in range(tokens))              # keys each prompt token sees in its chunk
+    causal = tokens * (tokens + 1) // 2
+    out["kupirax", "prefill", "local_attention_mma"] = ("tensor", 2.0 * H * seen * (d + dv))
+    out["llama", "prefill", "attention_prefill (tcgen05)"] = ("tensor", 2.0 * H * causal * 2 * d)
+    qkv = (H * d + G * d + G * dv) * 2
+    out["kupirax", "prefill", "local_attention_prepare"] = ("hbm", tokens * (2 * qkv))
+    out["llama", "prefill", "rope_cache_write"] = ("hbm", tokens * (2 * qkv))
+    out["kupirax", "decode", "local_attention_prepare"] = ("hbm", batch * (2 * qkv))
+    visible = min(context % C, context) + 1
+    out["kupirax", "decode", "local_attention"] = ("hbm", batch * visible * G * (d + dv) * 2)
+    out["llama", "decode", "attention_decode"] = ("hbm", batch * context * G * 2 * d * 2)
+    # state mixers: what a step must move at least - the float32 inputs and outputs of the recurrence per token,
+    # and in a decode step the state once in and once out
+    for kind, n, seqs in (("prefill", tokens, 1), ("decode", batch, batch)):
+        ret_io = n * Hr * (2 * dr + 2 * dvr) * 4
+        delta_io = n * H * (3 * d + 2 * dv + 1) * 4
+        ret_state, delta_state = seqs * Hr * dr * dvr * 8, seqs * H * d * dv * 8
+        out["kupirax", kind, "state_scan (retention)"] = ("hbm", ret_io + ret_state)
+        out["kupirax", kind, "state_scan (delta rule)"] = ("hbm", delta_io + delta_state)
+        out["kupirax", kind, "retention_prepare"] = ("hbm", n * Hr * (2 * dr + 2 * dvr) * 2 + n * Hr * (2 * dr + dvr) * 4)
+        out["kupirax", kind, "delta_prepare"] = ("hbm", n * (H * (2 * d + dv) * 2 + H * d * 4) + n * H * (3 * d + dv + 1) * 4)
+        out["kupirax", kind, "head_norm_gate"] = ("hbm", n * H * dv * (4 + 2 + 2))
+    return out
+
+
+def bench_design(args):
+    """Prompt and decode throughput of the Kupirax decoder and of the Llama decoder at equal width, feed-forward,
+    heads and layer count (random bfloat16 weights), and the device time of each of this library's kernels in one
+    prompt step and one decode step of either, with the fraction of the measured peak it reaches."""
+    import numpy as np
+    import torch
+    import cpp_minilamma_b200 as ml
+    from cpp_minilamma_b200 import StepEntry
+    peaks = load_peaks()
+    warmup, steps = max(args.warmup, 3), max(min(args.steps, 64), 8)
+    tokens, batch, context = PREFILL_TOKENS, 64, 1024
+    result = {"design": "kupirax", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+              "prefill_tokens": tokens, "decode_prompts": "uniform[128,1024)", "steps": steps, "warmup": warmup,
+              "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": peaks["source"]},
+              "sizes": {}}
+    for size in ([args.size] if args.size else list(DESIGN_SIZES)):
+        entry = {}
+        expected = design_rooflines(size, tokens, batch, context, peaks)
+        for model, cfg in (("kupirax", kupirax_config(size)), ("llama", llama_like_config(size))):
+            llm = ml.random_model(cfg, seed=0, dtype="bfloat16", max_tokens=batch * 1536 + 8192, max_positions=4096,
+                                  max_seqs=batch, max_step_tokens=8192)
+            numbers = {"layers": len(llm.model.spec.schedule), "parameters": llm.model.parameter_count()}
+            ms = time_prefill(llm, tokens, reps=5, warmup=3, seed=3)
+            numbers["prefill_tok_s"] = round(tokens * 1000.0 / ms, 1)
+            numbers["prefill_ms"] = round(ms, 3)
+            for b in (8, batch):
+                d_ms, _, launches, _, _ = time_decode(llm, b, steps, warmup, seed=30 + b, prompt_range=(128, 1024),
+                                                      repeats=3, context=4096)
+                numbers[f"decode_b{b}_tok_s"] = round(b * 1000.0 / d_ms, 1)
+                numbers[f"decode_b{b}_ms"] = round(d_ms, 4)
+                numbers[f"decode_b{b}_launches"] = round(launches, 1)
+            rng = np.random.RandomState(7)
+            draw = lambda n: [int(t) for t in rng.randint(0, cfg.vocab_size, size=n)]
+
+            def prompt_step():
+                slot, = llm.engine.acquire(1)
+                return [slot], [StepEntry(slot, draw(tokens), [tokens - 1])]
+
+            kernels = {"prefill": kernel_times_of_a_step(llm, prompt_step)}
+            slots = llm.engine.acquire(batch)
+            llm.engine.step_borrowed([StepEntry(s, draw(context), [context - 1]) for s in slots])
+            kernels["decode"] = kernel_times_of_a_step(llm, lambda: ([], [StepEntry(s, [5], [0]) for s in slots]))
+            for s in slots:
+                llm.engine.release(s)
+            table = {}
+            for kind, totals in kernels.items():
+                for name, (calls, total_ms) in sorted(totals.items()):
+                    row = {"calls": calls, "us_per_call": round(1000.0 * total_ms / calls, 2)}
+                    table[f"{kind}: {name}"] = row
+            entry[model] = numbers
+            entry[model]["kernels"] = table
+            for (m, kind, name), (bound, amount) in expected.items():
+                if m != model:
+                    continue
+                for key in [k for k in table if k.startswith(f"{kind}: {name}")]:
+                    us = table[key]["us_per_call"]
+                    peak = peaks["hbm_gbs"] * 1e9 if bound == "hbm" else peaks["bf16_tflops"] * 1e12
+                    table[key].update(bound=bound, frac=round(amount / (us * 1e-6) / peak, 4))
+            release_model(llm)
+        result["sizes"][size] = entry
+    print(json.dumps(result))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -412,6 +571,10 @@ def main():
     parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31_8b", help="model shape of the --profile step")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode step")
     parser.add_argument("--context", type=int, default=1024, help="prompt length of the --profile decode step")
+    parser.add_argument("--design", choices=["kupirax"], default=None,
+                        help="instead of the default workload: prompt and decode throughput and kernel times of that "
+                             "decoder beside the Llama decoder at equal sizes")
+    parser.add_argument("--size", choices=sorted(DESIGN_SIZES), default=None, help="one size of --design (default: all)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -426,6 +589,8 @@ def main():
     import cpp_minilamma_b200 as ml
     if args.profile:
         return profile_region(args)
+    if args.design:
+        return bench_design(args)
     sampler = ClockSampler()
     sampler.start()  # nvidia-smi needs a moment before its first line: it runs through the set-up
     warmup = max(args.warmup, 3)

@@ -173,6 +173,10 @@ class KupiraxConfig(ModelConfig):
             raise ConfigError(f"config.json: loop [{self.loop_start}, {self.loop_stop}) does not lie inside the "
                               f"{len(self.layers)} layers")
 
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
     def schedule(self) -> List[int]:
         """Layer indices in the order they run."""
         n = len(self.layers)

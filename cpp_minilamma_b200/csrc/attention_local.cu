@@ -10,9 +10,9 @@
 //     projection (all heads at once) and multiplied by a weight, the pairs of the first `rot`
 //     dimensions of every head are rotated by position * frequency (cos / sin from a table), q goes to
 //     a buffer and k, v into the pages of the cache.  All arithmetic in float32.
-//   * attend: one warp per (token, query head).  Lanes take one key each for the scores (float32 dot
-//     products over the head), the softmax runs online in float32, and for the values every lane owns
-//     output columns lane, lane + 32, ...  Any d and dv (16-byte loads where rows allow them).
+//   * attend: one block per (token, kv head) and the query heads of its group.  Pages of keys and values pass
+//     through shared memory; scores are float32 dot products over the head, the softmax runs online in
+//     float32.  Any d and dv (16-byte copies where rows are whole 16-byte words).
 #include "common.cuh"
 
 namespace mll {
@@ -96,6 +96,29 @@ __global__ void __launch_bounds__(256) local_prepare_kernel(LocalPrepArgs a) {
   }
 }
 
+template <typename T>
+struct Vec16;  // 16 bytes of T as floats
+template <>
+struct Vec16<float> {
+  static __device__ __forceinline__ void load(const float* p, float* out) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      out[2 * i] = f.x;
+      out[2 * i + 1] = f.y;
+    }
+  }
+};
+
 struct LocalAttnArgs {
   const void* q;         // [T, Hq * d]
   const void* k_cache;
@@ -109,124 +132,200 @@ struct LocalAttnArgs {
   float scale;
 };
 
-template <typename T>
-__device__ __forceinline__ float dot_row(const T* __restrict__ k, const float* __restrict__ q, int d, bool vec);
-
-template <>
-__device__ __forceinline__ float dot_row<float>(const float* __restrict__ k, const float* __restrict__ q, int d,
-                                                bool vec) {
-  float s = 0.f;
-  if (vec) {
-    for (int e = 0; e < d; e += 4) {
-      const float4 kv = *reinterpret_cast<const float4*>(k + e);
-      const float4 qv = *reinterpret_cast<const float4*>(q + e);
-      s = fmaf(kv.x, qv.x, s); s = fmaf(kv.y, qv.y, s); s = fmaf(kv.z, qv.z, s); s = fmaf(kv.w, qv.w, s);
-    }
-  } else {
-    for (int e = 0; e < d; ++e) s = fmaf(k[e], q[e], s);
-  }
-  return s;
-}
-
-template <>
-__device__ __forceinline__ float dot_row<__nv_bfloat16>(const __nv_bfloat16* __restrict__ k,
-                                                        const float* __restrict__ q, int d, bool vec) {
-  float s = 0.f;
-  if (vec) {
-    for (int e = 0; e < d; e += 8) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(k + e);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h[i]);
-        s = fmaf(f.x, q[e + 2 * i], s);
-        s = fmaf(f.y, q[e + 2 * i + 1], s);
-      }
-    }
-  } else {
-    for (int e = 0; e < d; ++e) s = fmaf(__bfloat162float(k[e]), q[e], s);
-  }
-  return s;
-}
-
-constexpr int LOCAL_WARPS = 4;
-
-// grid (ceil(T / LOCAL_WARPS), Hq); dynamic shared memory LOCAL_WARPS * d_padded floats.
+// grid (tokens, Hk * head chunks), 128 threads.  A block owns one token, one kv head and up to `hpb` of the
+// query heads that read it; it walks the pages that hold keys first .. pos.  A page's keys and values are
+// brought into shared memory by all threads (16-byte asynchronous copies where rows are whole 16-byte words,
+// two pages in flight where shared memory allows), so that the loads of a page are all in flight together
+// and every key and value is read once for the heads of its group.
 template <typename T, int NACC>
-__global__ void __launch_bounds__(32 * LOCAL_WARPS) local_attention_kernel(LocalAttnArgs a) {
-  extern __shared__ __align__(16) float q_smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * LOCAL_WARPS + warp;
-  if (t >= a.n_tokens) return;  // whole warps leave; nothing below synchronises the block
-  const int h = blockIdx.y;
-  const int kvh = h / (a.n_heads / a.n_kv_heads);
+__global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, int hpb, int stages, int vec) {
   const int d = a.d, dv = a.dv;
-  const int d_pad = (d + 3) & ~3;
-  float* qs = q_smem + warp * d_pad;
-  const T* qrow = (const T*)a.q + ((size_t)t * a.n_heads + h) * d;
-  for (int e = lane; e < d; e += 32) qs[e] = to_float(qrow[e]) * a.scale;
-  __syncwarp();
+  const int group = a.n_heads / a.n_kv_heads;
+  const int chunks = (group + hpb - 1) / hpb;
+  const int t = blockIdx.x;
+  const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * hpb;
+  const int ng = min(hpb, group - g0);
+  const int h0 = kvh * group + g0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pos = a.tok_pos[t];
   int first = a.chunk > 0 ? (pos / a.chunk) * a.chunk : 0;
   if (a.window > 0) first = max(first, pos - a.window + 1);
   const int* table = a.block_table + (size_t)a.seq_slot[a.tok_seq[t]] * a.max_blocks;
-  const bool kvec = (d * sizeof(T)) % 16 == 0;
 
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int PAD = 16 / sizeof(T);
+  const int d_pad = (d + 3) & ~3;
+  float* q_s = reinterpret_cast<float*>(smem_raw);   // [hpb][d_pad], scaled
+  float* s_s = q_s + hpb * d_pad;                     // [hpb][PAGE]
+  float* m_s = s_s + hpb * MLL_PAGE;                  // [hpb] running maximum, sum, rescale factor
+  float* l_s = m_s + hpb;
+  float* alpha_s = l_s + hpb;
+  size_t off = (size_t)((alpha_s + hpb) - q_s) * sizeof(float);
+  off = (off + 15) & ~(size_t)15;
+  const int k_stride = ((d + PAD - 1) / PAD) * PAD + PAD;  // elements; rows start on 16-byte boundaries
+  const int v_stride = ((dv + PAD - 1) / PAD) * PAD;
+  const size_t k_tile = (size_t)MLL_PAGE * k_stride, v_tile = (size_t)MLL_PAGE * v_stride;
+  T* k_s = reinterpret_cast<T*>(smem_raw + off);
+  T* v_s = k_s + stages * k_tile;
+
+  for (int i = tid; i < ng * d; i += 128) {
+    const int g = i / d, e = i % d;
+    q_s[g * d_pad + e] = to_float(((const T*)a.q)[((size_t)t * a.n_heads + h0 + g) * d + e]) * a.scale;
+  }
+  for (int i = tid; i < ng; i += 128) {
+    m_s[i] = -INFINITY;
+    l_s[i] = 0.f;
+  }
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-  for (int j0 = first; j0 <= pos; j0 += 32) {
-    const int j = j0 + lane;
-    const bool valid = j <= pos;
-    int page = 0;
-    float s = -INFINITY;
-    if (valid) {
-      page = table[j / MLL_PAGE];
-      const T* krow = (const T*)a.k_cache + (((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE + j % MLL_PAGE) * d;
-      s = dot_row<T>(krow, qs, d, kvec);
-    }
-    const float m_new = fmaxf(m_run, warp_max(s));  // lane 0 of the step is always valid: finite
-    const float alpha = expf(m_run - m_new);
-    const float p = valid ? expf(s - m_new) : 0.f;
-    l_run = l_run * alpha + warp_sum(p);
-    m_run = m_new;
-#pragma unroll
-    for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
-    const int count = min(32, pos - j0 + 1);
-    for (int jj = 0; jj < count; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const int pg = __shfl_sync(0xffffffffu, page, jj);
-      const T* vrow = (const T*)a.v_cache + (((size_t)pg * a.n_kv_heads + kvh) * MLL_PAGE + (j0 + jj) % MLL_PAGE) * dv;
-#pragma unroll
-      for (int i = 0; i < NACC; ++i) {
-        const int c = lane + 32 * i;
-        if (c < dv) acc[i] = fmaf(pj, to_float(vrow[c]), acc[i]);
+
+  const int p_begin = first / MLL_PAGE, p_end = pos / MLL_PAGE + 1;
+  auto load_tiles = [&](int page_index, int stage) {
+    const int page = table[page_index];
+    const T* kg = (const T*)a.k_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * d;
+    const T* vg = (const T*)a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * dv;
+    T* kd = k_s + stage * k_tile;
+    T* vd = v_s + stage * v_tile;
+    const int r_lo = max(0, first - page_index * MLL_PAGE), r_hi = min(MLL_PAGE, pos + 1 - page_index * MLL_PAGE);
+    if (vec) {
+      const int kc = d / PAD, vc = dv / PAD;
+      for (int c = tid; c < (r_hi - r_lo) * kc; c += 128) {
+        const int r = r_lo + c / kc, cc = c % kc;
+        cp_async16(kd + (size_t)r * k_stride + cc * PAD, kg + (size_t)r * d + cc * PAD);
+      }
+      for (int c = tid; c < (r_hi - r_lo) * vc; c += 128) {
+        const int r = r_lo + c / vc, cc = c % vc;
+        cp_async16(vd + (size_t)r * v_stride + cc * PAD, vg + (size_t)r * dv + cc * PAD);
+      }
+    } else {
+      for (int c = tid; c < (r_hi - r_lo) * d; c += 128) {
+        const int r = r_lo + c / d, e = c % d;
+        kd[(size_t)r * k_stride + e] = kg[(size_t)r * d + e];
+      }
+      for (int c = tid; c < (r_hi - r_lo) * dv; c += 128) {
+        const int r = r_lo + c / dv, e = c % dv;
+        vd[(size_t)r * v_stride + e] = vg[(size_t)r * dv + e];
       }
     }
+  };
+
+  load_tiles(p_begin, 0);
+  cp_async_commit();
+  for (int p = p_begin, it = 0; p < p_end; ++p, ++it) {
+    const int cur = stages == 2 ? (it & 1) : 0;
+    if (stages == 2 && p + 1 < p_end) {
+      load_tiles(p + 1, cur ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const T* kt = k_s + cur * k_tile;
+    const T* vt = v_s + cur * v_tile;
+    const int jlo = max(0, first - p * MLL_PAGE), jhi = min(MLL_PAGE, pos + 1 - p * MLL_PAGE);
+
+    for (int idx = tid; idx < ng * MLL_PAGE; idx += 128) {
+      const int g = idx / MLL_PAGE, j = idx % MLL_PAGE;
+      float sc = -INFINITY;
+      if (j >= jlo && j < jhi) {
+        const T* kr = kt + (size_t)j * k_stride;
+        const float* qg = q_s + g * d_pad;
+        float dot = 0.f;
+        if (vec) {
+          for (int e = 0; e < d; e += PAD) {
+            float kv[PAD];
+            Vec16<T>::load(kr + e, kv);
+#pragma unroll
+            for (int u = 0; u < PAD; ++u) dot = fmaf(qg[e + u], kv[u], dot);
+          }
+        } else {
+          for (int e = 0; e < d; ++e) dot = fmaf(qg[e], to_float(kr[e]), dot);
+        }
+        sc = dot;
+      }
+      s_s[idx] = sc;
+    }
+    __syncthreads();
+    for (int g = warp; g < ng; g += 4) {
+      const float v0 = s_s[g * MLL_PAGE + lane], v1 = s_s[g * MLL_PAGE + lane + 32];
+      const float m_old = m_s[g];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(v0, v1)));  // every page of the walk holds a visible key: finite
+      const float alpha = expf(m_old - m_new);
+      const float p0 = expf(v0 - m_new), p1 = expf(v1 - m_new);
+      s_s[g * MLL_PAGE + lane] = p0;
+      s_s[g * MLL_PAGE + lane + 32] = p1;
+      const float psum = warp_sum(p0 + p1);
+      if (lane == 0) {
+        l_s[g] = l_s[g] * alpha + psum;
+        m_s[g] = m_new;
+        alpha_s[g] = alpha;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int o = tid + 128 * i;
+      if (o < ng * dv) {
+        const int g = o / dv, e = o % dv;
+        float v = acc[i] * alpha_s[g];
+        const float* pg = s_s + g * MLL_PAGE;
+        for (int j = jlo; j < jhi; ++j) v = fmaf(pg[j], to_float(vt[(size_t)j * v_stride + e]), v);
+        acc[i] = v;
+      }
+    }
+    __syncthreads();
+    if (stages == 1 && p + 1 < p_end) {
+      load_tiles(p + 1, 0);
+      cp_async_commit();
+    }
   }
-  const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-  T* orow = (T*)a.out + ((size_t)t * a.n_heads + h) * dv;
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
-    const int c = lane + 32 * i;
-    if (c < dv) orow[c] = from_float<T>(acc[i] * inv);
+    const int o = tid + 128 * i;
+    if (o < ng * dv) {
+      const float l = l_s[o / dv];
+      ((T*)a.out)[((size_t)t * a.n_heads + h0) * dv + o] = from_float<T>(l > 0.f ? acc[i] / l : 0.f);
+    }
   }
 }
 
 template <typename T>
 int launch_local_attention(const LocalAttnArgs& a, cudaStream_t stream) {
-  const dim3 grid((a.n_tokens + LOCAL_WARPS - 1) / LOCAL_WARPS, a.n_heads);
-  const size_t smem = (size_t)LOCAL_WARPS * ((a.d + 3) & ~3) * sizeof(float);
-  const int nacc = (a.dv + 31) / 32;
-  if (nacc <= 1)
-    MLL_LAUNCH((local_attention_kernel<T, 1>), grid, 32 * LOCAL_WARPS, smem, stream, a);
-  else if (nacc <= 2)
-    MLL_LAUNCH((local_attention_kernel<T, 2>), grid, 32 * LOCAL_WARPS, smem, stream, a);
-  else if (nacc <= 4)
-    MLL_LAUNCH((local_attention_kernel<T, 4>), grid, 32 * LOCAL_WARPS, smem, stream, a);
-  else
-    MLL_LAUNCH((local_attention_kernel<T, 8>), grid, 32 * LOCAL_WARPS, smem, stream, a);
+  constexpr int PAD = 16 / sizeof(T);
+  const int group = a.n_heads / a.n_kv_heads;
+  const int hpb = max(1, min(group, 1024 / a.dv));       // at most 8 accumulators a thread
+  const int chunks = (group + hpb - 1) / hpb;
+  const int vec = (a.d % PAD == 0 && a.dv % PAD == 0) ? 1 : 0;
+  const int k_stride = ((a.d + PAD - 1) / PAD) * PAD + PAD, v_stride = ((a.dv + PAD - 1) / PAD) * PAD;
+  size_t fixed = (size_t)(hpb * ((a.d + 3) & ~3) + hpb * MLL_PAGE + 3 * hpb) * sizeof(float);
+  fixed = (fixed + 15) & ~(size_t)15;
+  const size_t tile = (size_t)MLL_PAGE * (k_stride + v_stride) * sizeof(T);
+  const int stages = fixed + 2 * tile <= 96 * 1024 ? 2 : 1;
+  const size_t smem = fixed + stages * tile;
+  MLL_REQUIRE(smem <= 200 * 1024, "local attention: head sizes %d / %d need %zu bytes of shared memory", a.d, a.dv, smem);
+  MLL_REQUIRE((long long)a.n_kv_heads * chunks <= 65535, "local attention: too many heads for one launch");
+  const dim3 grid(a.n_tokens, a.n_kv_heads * chunks);
+  const int nacc = (hpb * a.dv + 127) / 128;
+#define MLL_LOCAL_LAUNCH(N)                                                                                   \
+  do {                                                                                                        \
+    auto kernel = local_attention_kernel<T, N>;                                                               \
+    if (smem > 48 * 1024) {                                                                                   \
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (err != cudaSuccess) {                                                                               \
+        mll_set_error("local attention: cannot reserve %zu bytes of shared memory: %s", smem,                 \
+                      cudaGetErrorString(err));                                                               \
+        return (int)err;                                                                                      \
+      }                                                                                                       \
+    }                                                                                                         \
+    MLL_LAUNCH((kernel), grid, 128, smem, stream, a, hpb, stages, vec);                                       \
+  } while (0)
+  if (nacc <= 1) MLL_LOCAL_LAUNCH(1);
+  else if (nacc <= 2) MLL_LOCAL_LAUNCH(2);
+  else if (nacc <= 4) MLL_LOCAL_LAUNCH(4);
+  else MLL_LOCAL_LAUNCH(8);
+#undef MLL_LOCAL_LAUNCH
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -262,9 +361,8 @@ MLL_API int mll_local_attention(const void* q, const void* k_cache, const void* 
                                 int n_tokens, int n_heads, int n_kv_heads, int d, int dv, int chunk, int window,
                                 int max_blocks, float scale, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention: bad head counts");
-  MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0 && dv <= 256, "local attention: head sizes %d / %d (at most 1024 / 256)", d, dv);
+  MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0 && dv <= 1024, "local attention: head sizes %d / %d (at most 1024)", d, dv);
   MLL_REQUIRE(chunk >= 0 && window >= 0, "local attention: negative chunk or window");
-  MLL_REQUIRE(n_heads <= 65535, "local attention: too many heads for one launch");
   if (n_tokens == 0) return 0;
   mll::LocalAttnArgs a{q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_tokens, n_heads,
                        n_kv_heads, d, dv, chunk, window, max_blocks, scale};

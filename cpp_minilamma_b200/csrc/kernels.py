@@ -56,8 +56,52 @@ launches = 0  # kernels of this library launched so far (counted per successful 
 calls: Dict[str, int] = {}  # the same, per kind of launch (the name each wrapper gives its kernel)
 
 
+class KernelTimes:
+    """Device time of every launch made through this module while the object is the active timer: a CUDA event
+    is recorded on the launching stream before and after each call (`with KernelTimes() as times: ...`;
+    `times.totals()` waits for the device and gives {kernel: (calls, milliseconds)})."""
+
+    def __init__(self):
+        self.events = []
+        self._open = None
+
+    def __enter__(self):
+        global _timer
+        _timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = None
+
+    def begin(self):
+        self._open = torch.cuda.Event(enable_timing=True)
+        self._open.record()
+
+    def end(self, what: str):
+        if self._open is not None:
+            done = torch.cuda.Event(enable_timing=True)
+            done.record()
+            self.events.append((what, self._open, done))
+            self._open = None
+
+    def totals(self):
+        torch.cuda.synchronize()
+        out: Dict[str, list] = {}
+        for what, first, last in self.events:
+            entry = out.setdefault(what, [0, 0.0])
+            entry[0] += 1
+            entry[1] += first.elapsed_time(last)
+        return {k: (v[0], v[1]) for k, v in out.items()}
+
+
+_timer: Optional[KernelTimes] = None
+
+
 def _check(code: int, what: str, kernels: int = 1) -> None:
     global launches
+    if _timer is not None:
+        _timer.end(what)
     launches += kernels
     calls[what] = calls.get(what, 0) + 1
     if code != 0:
@@ -66,6 +110,9 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 
 
 def _stream() -> ctypes.c_void_p:
+    # every wrapper evaluates this once, among the arguments of its launch: the place where a timer's first event goes
+    if _timer is not None:
+        _timer.begin()
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -970,7 +1017,8 @@ def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, s
     _check(lib().mll_state_scan(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(head_decay), _ptr(state), _ptr(out), _ptr(seq_slot),
         _ptr(seq_qstart), _ptr(seq_qlen), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
-        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(int(delta)), _stream()), "state_scan")
+        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(int(delta)), _stream()),
+        "state_scan (delta rule)" if delta else "state_scan (retention)")
 
 
 GATE_SILU, GATE_SIGMOID = 0, 1

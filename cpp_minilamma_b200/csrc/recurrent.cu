@@ -93,18 +93,25 @@ struct DeltaPrepArgs {
   float unit_eps;
 };
 
-// one block per token; dynamic shared memory: C floats
+// grid (tokens, 2 G + H), 128 threads: a block owns one head of one token - a q head, a k head, or a value head
+// together with that head's beta and decays.  Dynamic shared memory: max(d, dv) floats.
 template <typename T>
-__global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepArgs a) {
+__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepArgs a) {
   extern __shared__ float conv_out[];
-  const int t = blockIdx.x;
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, unit = blockIdx.y;
   const int H = a.n_heads, G = a.n_kv_heads, d = a.d, dv = a.dv, taps = a.taps;
   const int nqk = G * d, C = 2 * nqk + H * dv;
   const int seq = a.tok_seq[t];
   const int local = t - a.seq_qstart[seq];  // index among this step's tokens of the sequence
   const float* state = a.conv_state + (size_t)a.seq_slot[seq] * (taps - 1) * C;
   const T* proj = (const T*)a.proj;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const bool is_v = unit >= 2 * G;
+  const int width = is_v ? dv : d;
+  const int c0 = is_v ? 2 * nqk + (unit - 2 * G) * dv : unit * d;  // first channel of the head
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    const int c = c0 + e;
     float y = 0.f;
     for (int back = 0; back < taps; ++back) {  // the input `back` tokens ago meets tap taps - 1 - back
       float x;
@@ -114,28 +121,27 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepArgs a) {
         x = state[(size_t)(local - back + taps - 1) * C + c];
       y = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - back)], x, y);
     }
-    conv_out[c] = silu_f(y);
+    y = silu_f(y);
+    conv_out[e] = y;
+    ss += y * y;
   }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-  // q and k heads: unit length (and q / sqrt(d)); one warp per head
-  for (int hd = warp; hd < 2 * G; hd += n_warps) {
-    const float* x = conv_out + hd * d;
-    float ss = 0.f;
-    for (int e = lane; e < d; e += 32) ss += x[e] * x[e];
-    ss = warp_sum(ss);
-    const bool is_q = hd < G;
-    const float f = (is_q ? rsqrtf((float)d) : 1.f) / sqrtf(ss + a.unit_eps);
-    float* dst = (is_q ? a.q : a.k) + ((size_t)t * G + (is_q ? hd : hd - G)) * d;
-    for (int e = lane; e < d; e += 32) dst[e] = x[e] * f;
+  if (is_v) {
+    const int h = unit - 2 * G;
+    __syncthreads();
+    for (int e = threadIdx.x; e < dv; e += blockDim.x) a.v[((size_t)t * H + h) * dv + e] = conv_out[e];
+    if (threadIdx.x == 0) a.beta[(size_t)t * H + h] = sigmoid_f(to_float(proj[(size_t)t * a.ld + C + h]));
+    const float rate = expf(a.a_log[h]);
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+      const float sp = softplus_f(a.rate[(size_t)t * a.rate_ld + h * d + e] + a.dt_bias[h * d + e]);
+      a.g[((size_t)t * H + h) * d + e] = expf(-rate * sp);
+    }
+    return;
   }
-  for (int i = threadIdx.x; i < H * dv; i += blockDim.x) a.v[(size_t)t * H * dv + i] = conv_out[2 * nqk + i];
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    a.beta[(size_t)t * H + i] = sigmoid_f(to_float(proj[(size_t)t * a.ld + C + i]));
-  for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
-    const float sp = softplus_f(a.rate[(size_t)t * a.rate_ld + i] + a.dt_bias[i]);
-    a.g[(size_t)t * H * d + i] = expf(-expf(a.a_log[i / d]) * sp);
-  }
+  ss = block_sum(ss, scratch);  // q and k heads: unit length (and q / sqrt(d))
+  const bool is_q = unit < G;
+  const float f = (is_q ? rsqrtf((float)d) : 1.f) / sqrtf(ss + a.unit_eps);
+  float* dst = (is_q ? a.q : a.k) + ((size_t)t * G + (is_q ? unit : unit - G)) * d;
+  for (int e = threadIdx.x; e < d; e += blockDim.x) dst[e] = conv_out[e] * f;
 }
 
 // grid (ceil(C / 128), sequences): new state = the last taps - 1 of (old state, this step's inputs)
@@ -174,9 +180,16 @@ struct ScanArgs {
 
 constexpr int SCAN_THREADS = 128;
 
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem));
+}
+
 // grid (column tiles, H, sequences).  Lane layout inside a warp: lane = r * (32 / R) + c; lane (r, c) holds rows
 // r * ROWS .. r * ROWS + ROWS - 1 of column c of the warp's columns.  Rows past d are padding: their k and q
-// are staged as 0, so their S stays 0 and adds nothing.
+// are staged as 0, so their S stays 0 and adds nothing.  The tokens' q, k, g, v and beta arrive in shared memory
+// `tok_stage` tokens at a time through a two-stage ring of asynchronous copies, so that the next tokens load
+// while these are worked on and the chain from token to token is arithmetic only.
 template <int ROWS, int R, bool DELTA>
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
   extern __shared__ __align__(16) float stage[];
@@ -185,7 +198,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
   constexpr int CPB = CPW * (SCAN_THREADS / 32);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = lane / CPW, cw = lane % CPW;
-  const int col = blockIdx.x * CPB + warp * CPW + cw;
+  const int col0 = blockIdx.x * CPB;
+  const int col = col0 + warp * CPW + cw;
   const int h = blockIdx.y, seq = blockIdx.z;
   const int H = a.n_heads, G = a.n_kv_heads, d = a.d, dv = a.dv;
   const int kvh = h / (H / G);
@@ -199,49 +213,97 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     s[i] = (live && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
   const int TS = a.tok_stage;
-  float* q_s = stage;                 // [TS][DP]
-  float* k_s = q_s + TS * DP;
-  float* g_s = k_s + TS * DP;         // DELTA only
-  const float decay = DELTA ? 1.f : a.head_decay[h];
-  for (int t0 = 0; t0 < n_tok; t0 += TS) {
+  const int per_stage = (TS * DP * (DELTA ? 3 : 2) + TS * CPB + TS + 3) & ~3;  // stages start on 16-byte boundaries
+  // the padding rows of both stages, once: the copies below never touch them
+  for (int i = tid; i < 2 * TS * DP; i += SCAN_THREADS) {
+    const int st = i / (TS * DP), rest = i % (TS * DP);
+    if (rest % DP >= d) {
+      float* base = stage + st * per_stage;
+      base[rest] = 0.f;
+      base[TS * DP + rest] = 0.f;
+      if (DELTA) base[2 * TS * DP + rest] = 1.f;
+    }
+  }
+  auto load = [&](int t0, int st) {
     const int nt = min(TS, n_tok - t0);
-    __syncthreads();
-    for (int i = tid; i < nt * DP; i += SCAN_THREADS) {
-      const int tt = i / DP, e = i % DP;
-      const size_t tok = (size_t)(row0 + t0 + tt);
-      const bool in = e < d;
-      q_s[i] = in ? a.q[(tok * G + kvh) * d + e] : 0.f;
-      k_s[i] = in ? a.k[(tok * G + kvh) * d + e] : 0.f;
-      if (DELTA) g_s[i] = in ? a.g[(tok * H + h) * d + e] : 1.f;
+    float* q_s = stage + st * per_stage;
+    float* k_s = q_s + TS * DP;
+    float* g_s = k_s + TS * DP;
+    float* v_s = stage + st * per_stage + TS * DP * (DELTA ? 3 : 2);
+    float* b_s = v_s + TS * CPB;
+    if ((d & 3) == 0) {  // rows are whole 16-byte words
+      const int words = d >> 2;
+      for (int i = tid; i < nt * words; i += SCAN_THREADS) {
+        const int tt = i / words, e = (i % words) << 2;
+        const size_t tok = (size_t)(row0 + t0 + tt);
+        cp_async16(q_s + tt * DP + e, a.q + (tok * G + kvh) * d + e);
+        cp_async16(k_s + tt * DP + e, a.k + (tok * G + kvh) * d + e);
+        if (DELTA) cp_async16(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
+      }
+    } else {
+      for (int i = tid; i < nt * d; i += SCAN_THREADS) {
+        const int tt = i / d, e = i % d;
+        const size_t tok = (size_t)(row0 + t0 + tt);
+        cp_async4(q_s + tt * DP + e, a.q + (tok * G + kvh) * d + e);
+        cp_async4(k_s + tt * DP + e, a.k + (tok * G + kvh) * d + e);
+        if (DELTA) cp_async4(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
+      }
+    }
+    for (int i = tid; i < nt * CPB; i += SCAN_THREADS) {
+      const int tt = i / CPB, c = i % CPB;
+      if (col0 + c < dv) cp_async4(v_s + i, a.v + ((size_t)(row0 + t0 + tt) * H + h) * dv + col0 + c);
+    }
+    if (DELTA)
+      for (int i = tid; i < nt; i += SCAN_THREADS) cp_async4(b_s + i, a.beta + (size_t)(row0 + t0 + i) * H + h);
+  };
+  const float decay = DELTA ? 1.f : a.head_decay[h];
+  load(0, 0);
+  cp_async_commit();
+  for (int t0 = 0, it = 0; t0 < n_tok; t0 += TS, ++it) {
+    const int st = it & 1;
+    if (t0 + TS < n_tok) {
+      load(t0 + TS, st ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
+    const int nt = min(TS, n_tok - t0);
+    const float* q_s = stage + st * per_stage;
+    const float* k_s = q_s + TS * DP;
+    const float* g_s = k_s + TS * DP;
+    const float* v_s = stage + st * per_stage + TS * DP * (DELTA ? 3 : 2);
+    const float* b_s = v_s + TS * CPB;
     for (int tt = 0; tt < nt; ++tt) {
-      const size_t tok = (size_t)(row0 + t0 + tt);
       const float* qv = q_s + tt * DP + r * ROWS;
       const float* kv = k_s + tt * DP + r * ROWS;
-      float u = live ? a.v[(tok * H + h) * dv + col] : 0.f;
+      float u = live ? v_s[tt * CPB + warp * CPW + cw] : 0.f;
       if (DELTA) {
         const float* gv = g_s + tt * DP + r * ROWS;
-        float part = 0.f;
+        float p4[4] = {0.f, 0.f, 0.f, 0.f};  // four sums side by side: the chain of additions is a quarter as long
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
           s[i] *= gv[i];
-          part = fmaf(s[i], kv[i], part);
+          p4[i & 3] = fmaf(s[i], kv[i], p4[i & 3]);
         }
+        float part = (p4[0] + p4[1]) + (p4[2] + p4[3]);
 #pragma unroll
         for (int o = CPW; o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        u = a.beta[tok * H + h] * (u - part);
+        u = b_s[tt] * (u - part);
       }
-      float o_part = 0.f;
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < ROWS; ++i) {
         s[i] = DELTA ? fmaf(kv[i], u, s[i]) : fmaf(decay, s[i], kv[i] * u);
-        o_part = fmaf(s[i], qv[i], o_part);
+        o4[i & 3] = fmaf(s[i], qv[i], o4[i & 3]);
       }
+      float o_part = (o4[0] + o4[1]) + (o4[2] + o4[3]);
 #pragma unroll
       for (int o = CPW; o < 32; o <<= 1) o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
-      if (live && r == 0) a.out[(tok * H + h) * dv + col] = o_part;
+      if (live && r == 0) a.out[((size_t)(row0 + t0 + tt) * H + h) * dv + col] = o_part;
     }
+    __syncthreads();  // this stage is loaded again two rounds on
   }
   if (live) {
 #pragma unroll
@@ -256,22 +318,31 @@ template <int ROWS, int R, bool DELTA>
 int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
   ScanArgs a = args;
   constexpr int DP = ROWS * R, CPB = (32 / R) * (SCAN_THREADS / 32);
-  a.tok_stage = DP <= 128 ? 16 : (DP <= 256 ? 8 : 4);
-  const size_t smem = (size_t)a.tok_stage * DP * (DELTA ? 3 : 2) * sizeof(float);
+  a.tok_stage = DP <= 64 ? 16 : (DP <= 128 ? 8 : (DP <= 256 ? 4 : (DP <= 512 ? 2 : 1)));
+  const size_t smem = (size_t)2 * ((a.tok_stage * DP * (DELTA ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
   const dim3 grid((a.dv + CPB - 1) / CPB, a.n_heads, n_seqs);
   MLL_LAUNCH((state_scan_kernel<ROWS, R, DELTA>), grid, SCAN_THREADS, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
 
+// How a column of S is spread over lanes.  With enough columns to fill the device (a decode step of a batch) a
+// thread holds a whole column (keys up to 128; two lanes up to 256): a warp then reads and writes 128
+// consecutive bytes of every row of the state, and nothing crosses lanes.  Otherwise (a prompt of one or a few
+// sequences) eight lanes share a column, so that eight times as many threads work on the chain from token
+// to token.
 template <bool DELTA>
 int dispatch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
   const int d = a.d;
-  if (d <= 32) return launch_scan<8, 4, DELTA>(a, n_seqs, stream);
-  if (d <= 64) return launch_scan<16, 4, DELTA>(a, n_seqs, stream);
-  if (d <= 128) return launch_scan<32, 4, DELTA>(a, n_seqs, stream);
+  const bool many = (long long)n_seqs * a.n_heads * a.dv >= (long long)mll_sm_count() * 512;
+  if (many && d <= 32) return launch_scan<32, 1, DELTA>(a, n_seqs, stream);
+  if (many && d <= 64) return launch_scan<64, 1, DELTA>(a, n_seqs, stream);
+  if (many && d <= 128) return launch_scan<64, 2, DELTA>(a, n_seqs, stream);
+  if (many && d <= 256) return launch_scan<64, 4, DELTA>(a, n_seqs, stream);
+  if (d <= 32) return launch_scan<4, 8, DELTA>(a, n_seqs, stream);
+  if (d <= 64) return launch_scan<8, 8, DELTA>(a, n_seqs, stream);
+  if (d <= 128) return launch_scan<16, 8, DELTA>(a, n_seqs, stream);
   if (d <= 256) return launch_scan<32, 8, DELTA>(a, n_seqs, stream);
-  if (d <= 512) return launch_scan<32, 16, DELTA>(a, n_seqs, stream);
   return launch_scan<32, 32, DELTA>(a, n_seqs, stream);
 }
 
@@ -330,22 +401,18 @@ MLL_API int mll_delta_prepare(const void* proj, const float* rate, const float* 
   MLL_REQUIRE(d > 0 && dv > 0 && taps >= 1, "delta prepare: bad sizes");
   const int C = 2 * n_kv_heads * d + n_heads * dv;
   MLL_REQUIRE(ld >= C + n_heads && rate_ld >= n_heads * d, "delta prepare: row strides %d / %d too short", ld, rate_ld);
-  MLL_REQUIRE((size_t)C * sizeof(float) <= 200 * 1024, "delta prepare: %d convolution channels exceed shared memory", C);
+  MLL_REQUIRE(d <= 8192 && dv <= 8192 && 2 * n_kv_heads + n_heads <= 65535, "delta prepare: heads too large or too many");
   if (n_tokens == 0) return 0;
   mll::DeltaPrepArgs a{proj, rate, conv_w, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, v, g, beta,
                        ld, rate_ld, n_heads, n_kv_heads, d, dv, taps, unit_eps};
-  const size_t smem = (size_t)C * sizeof(float);
-  if (dtype == MLL_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(mll::delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    MLL_LAUNCH((mll::delta_prepare_kernel<float>), n_tokens, 256, smem, stream, a);
-  } else if (dtype == MLL_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(mll::delta_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, a);
-  } else {
+  const size_t smem = (size_t)(d > dv ? d : dv) * sizeof(float);
+  const dim3 grid(n_tokens, 2 * n_kv_heads + n_heads);
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::delta_prepare_kernel<float>), grid, 128, smem, stream, a);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), grid, 128, smem, stream, a);
+  else
     MLL_REQUIRE(false, "delta prepare: unknown dtype %d", dtype);
-  }
   MLL_LAUNCH_CHECK();
   return 0;
 }

@@ -272,3 +272,57 @@ def test_tensor_core_prompt_kernel_against_the_general_one(d, dv, chunk, window)
     err = (fast.float() - plain.float()).abs()
     assert torch.isfinite(fast.float()).all()
     assert err.max().item() <= 0.03 * plain.float().abs().max().item(), (err.max().item(), int(err.argmax()) // (H * dv))
+
+
+@pytest.mark.parametrize("delta", [False, True])
+@pytest.mark.parametrize("n_seqs,H,G,d,dv", [(3, 2, 1, 24, 40),        # few columns: eight lanes share a column
+                                             (96, 8, 4, 20, 100),      # a batch that fills the device: a thread a column
+                                             (80, 8, 8, 72, 136),      # ... two lanes a column
+                                             (40, 8, 2, 200, 256),     # ... four lanes a column
+                                             (2, 1, 1, 300, 8)])       # keys beyond 256
+def test_state_scan_against_the_recurrence_written_out(delta, n_seqs, H, G, d, dv):
+    """The scan kernel alone, both rules and every way it spreads a column over lanes: sequences of one to four
+    tokens from a non-zero state, against S <- g S + k u^T, o = S^T q in float64."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(n_seqs * 7 + d)
+    lens = [1 + (i % 4) for i in range(n_seqs)]
+    T = sum(lens)
+    slots = list(range(n_seqs - 1, -1, -1))   # slot != sequence index
+    q = torch.randn((T, G * d), generator=gen)
+    k = torch.randn((T, G * d), generator=gen) / d ** 0.5
+    v = torch.randn((T, H * dv), generator=gen)
+    g = torch.rand((T, H * d), generator=gen) * 0.5 + 0.5
+    beta = torch.rand((T, H), generator=gen)
+    decay = torch.rand((H,), generator=gen) * 0.5 + 0.5
+    state = torch.randn((n_seqs + 1, H, d, dv), generator=gen)
+    want_o = torch.zeros((T, H * dv), dtype=torch.float64)
+    want_s = state.double().clone()
+    at = 0
+    for s, n in enumerate(lens):
+        for t in range(at, at + n):
+            for h in range(H):
+                S = want_s[slots[s], h]
+                qh, kh = q[t].double().view(G, d)[h // (H // G)], k[t].double().view(G, d)[h // (H // G)]
+                vh = v[t].double().view(H, dv)[h]
+                if delta:
+                    S = g[t].double().view(H, d)[h][:, None] * S
+                    u = beta[t, h].double() * (vh - S.T @ kh)
+                else:
+                    S = decay[h].double() * S
+                    u = vh
+                S = S + torch.outer(kh, u)
+                want_s[slots[s], h] = S
+                want_o[t].view(H, dv)[h] = S.T @ qh
+        at += n
+    step = make_step_state(dev, slots, [0] * n_seqs, lens)
+    out = torch.zeros((T, H * dv), dtype=torch.float32, device=dev)
+    state_dev = state.to(dev)
+    K.state_scan(q.to(dev), k.to(dev), v.to(dev), g.to(dev) if delta else None, beta.to(dev) if delta else None,
+                 None if delta else decay.to(dev), state_dev, out, step.seq_slot, step.seq_qstart, step.seq_qlen,
+                 n_seqs, H, G, d, dv)
+    torch.cuda.synchronize()
+    scale = max(1.0, want_o.abs().max().item())
+    assert (out.cpu().double() - want_o).abs().max().item() <= 2e-5 * scale
+    assert (state_dev.cpu().double() - want_s).abs().max().item() <= 2e-5 * max(1.0, want_s.abs().max().item())
