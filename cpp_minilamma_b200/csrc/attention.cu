@@ -83,7 +83,7 @@ attn_decode_kernel(AttnArgs a, int two_stage) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   const int ctx = a.seq_ctx[b];
-  const int first_key = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int first_key = decode_first_key(ctx, a.window);
   const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
   const int first_page = first_key / MLL_PAGE;
   const int per_split = (pages_total - first_page + a.n_splits - 1) / a.n_splits;
@@ -502,12 +502,12 @@ int prefill_dispatch(const AttnArgs& a, int n_tiles, cudaStream_t stream) {
   return launch_prefill<T, 16>(a, n_tiles, stream);
 }
 
-static int check_common(const AttnArgs& a, const char* what) {
+static int check_common(const AttnArgs& a, const char* what, bool chunks_allowed = false) {
   MLL_REQUIRE(a.head_dim >= 16 && a.head_dim <= 256 && a.head_dim % 16 == 0,
               "%s: head_dim %d is not a multiple of 16 in [16, 256]", what, a.head_dim);
   MLL_REQUIRE(a.n_heads > 0 && a.n_kv_heads > 0 && a.n_heads % a.n_kv_heads == 0,
               "%s: %d heads are not a multiple of %d kv heads", what, a.n_heads, a.n_kv_heads);
-  MLL_REQUIRE(a.window >= 0, "%s: negative window", what);
+  MLL_REQUIRE(a.window >= 0 || chunks_allowed, "%s: negative window", what);  // decode: a negative window names a chunk
   return 0;
 }
 
@@ -527,7 +527,7 @@ MLL_API int mll_attn_decode(const void* q, const void* k_cache, const void* v_ca
   a.block_table = block_table; a.out = out;
   a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.max_blocks = max_blocks;
   a.n_splits = n_splits; a.window = window; a.scale = scale;
-  if (mll::check_common(a, "attention decode") != 0) return -1;
+  if (mll::check_common(a, "attention decode", true) != 0) return -1;
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode: bad batch or split count");
   MLL_REQUIRE(n_splits == 1 || scratch != nullptr, "attention decode: %d splits need scratch memory", n_splits);
   if (n_seqs == 0) return 0;

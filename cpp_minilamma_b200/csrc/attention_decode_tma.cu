@@ -346,7 +346,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int h0 = kvh * group + chunk * 16;
 
   const int ctx = a.seq_ctx[b];
-  const int first_key = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int first_key = decode_first_key(ctx, a.window);
   const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
   const int first_page = first_key / MLL_PAGE;
   // a sequence uses as many of the offered splits as its own length pays for (attention_decode.cuh)

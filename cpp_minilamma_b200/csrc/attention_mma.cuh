@@ -56,7 +56,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   const int h0 = kvh * group + chunk * 16;
 
   const int ctx = a.seq_ctx[b];
-  const int first_key = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int first_key = decode_first_key(ctx, a.window);
   const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
   const int first_page = first_key / MLL_PAGE;
   // The launch offers n_splits blocks per (sequence, kv head); a sequence uses as many of them as

@@ -63,6 +63,7 @@ struct PrefillTc5Args {
   const int* block_table;
   __nv_bfloat16* out;    // [T, Hq * d]
   int n_heads, n_kv_heads, max_blocks, window;
+  int chunk;  // > 0: key j is visible from query i only if j / chunk == i / chunk (chunks count from position 0)
   float scale_log2;
 };
 
@@ -336,7 +337,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   const int rows = min(A_ROWS, qlen - row0);
   const int pos0 = ctx - qlen + row0;
   const int* table = a.block_table + (size_t)a.seq_slot[seq] * a.max_blocks;
-  const int first_key = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  int first_key = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  if (a.chunk > 0) first_key = max(first_key, (pos0 / a.chunk) * a.chunk);  // of the tile's first row; later rows reach no further back
+  const int last_chunk_start = a.chunk > 0 ? ((pos0 + rows - 1) / a.chunk) * a.chunk : 0;
   const int p_first = first_key / MLL_PAGE, p_last = (pos0 + rows - 1) / MLL_PAGE;
   const int n_pages = p_last - p_first + 1;
 
@@ -456,12 +459,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       float s[MLL_PAGE];
       a_tmem_ld64(tmem_row + sb * MLL_PAGE, s);
       const int k0 = (p_first + i) * MLL_PAGE;
-      const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS;
+      const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS || k0 < last_chunk_start;
+      const int chunk_first = a.chunk > 0 ? (qpos / a.chunk) * a.chunk : 0;
       if (needs_mask) {
 #pragma unroll
         for (int c = 0; c < MLL_PAGE; ++c) {
           const int kpos = k0 + c;
-          const bool keep = r < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+          const bool keep = r < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window) && kpos >= chunk_first;
           s[c] = keep ? s[c] : -INFINITY;
         }
       }
@@ -615,11 +619,12 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
                                  const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
                                  const int* tile_row0, const int* block_table, void* out, int n_tokens,
                                  long long n_pages, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
-                                 int max_blocks, int window, float scale, cudaStream_t stream) {
+                                 int max_blocks, int window, int chunk, float scale, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_prefill_tc5_supported(MLL_BF16, head_dim), "attention prefill (tcgen05): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention prefill (tcgen05): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_tokens >= 0 && (long long)n_tiles * n_heads < (1ll << 31),
               "attention prefill (tcgen05): bad tile or head count");
+  MLL_REQUIRE(window >= 0 && chunk >= 0, "attention prefill (tcgen05): negative window or chunk");
   MLL_REQUIRE(n_pages > 0 && n_pages * n_kv_heads * MLL_PAGE < (1ll << 31),
               "attention prefill (tcgen05): %lld pages are more than the row coordinate holds", n_pages);
   MLL_REQUIRE(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16 == 0,
@@ -630,7 +635,7 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
   if (mll::tensor_map_bf16(k_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &kmap) != 0) return -1;
   if (mll::tensor_map_bf16(v_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &vmap) != 0) return -1;
   mll::PrefillTc5Args a{seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
-                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, scale * 1.4426950408889634f};
+                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, scale * 1.4426950408889634f};
   if (head_dim == 64) return mll::launch_prefill_tc5<64>(qmap, kmap, vmap, a, n_tiles, stream);
   return mll::launch_prefill_tc5<128>(qmap, kmap, vmap, a, n_tiles, stream);
 }

@@ -112,6 +112,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return total;
 }
 
+// First key that the one query token of a decode step may see, `ctx` being the sequence's length with that token.
+// window > 0: the last `window` positions.  window < 0 names a chunk of -window positions instead: the keys of
+// the query's own chunk, chunks counted from position 0 (the query sits at ctx - 1).
+__device__ __forceinline__ int decode_first_key(int ctx, int window) {
+  if (window > 0) return max(0, ctx - window);
+  if (window < 0) return ((ctx - 1) / -window) * -window;
+  return 0;
+}
+
 // 16-byte asynchronous copy global -> shared (both 16-byte aligned)
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 28
+ABI_VERSION = 29
 MAX_TOP_K = 1024
 
 
@@ -570,12 +570,18 @@ USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
                      scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None,
-                     work: Optional[torch.Tensor] = None) -> None:
+                     work: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
+    `chunk` > 0 (not together with a window): the query sees the keys of its own chunk of that many positions only,
+    chunks counted from position 0; the kernels take it as a negative window.
     bfloat16 runs on tensor cores (head sizes 16 .. 256 in steps of 16), float32 on the general kernel.
     `order`: optional int32 permutation of the sequences, longest context first; the TMA-fed kernel starts its
     blocks in that order so that short sequences fill the end of the launch (the others ignore it)."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
+    if chunk:
+        if chunk < 0 or window:
+            raise KernelError("attention decode: a chunk must be positive and comes without a window")
+        window = -chunk
     _need(seq_slot, "attention seq_slot", torch.int32, 1)
     _need(seq_ctx, "attention seq_ctx", torch.int32, 1)
     _need(block_table, "attention block_table", torch.int32, 2)
@@ -754,12 +760,20 @@ def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_c
 PREFILL_TILE = 64  # query rows per entry of the work list that `attention_prefill` takes
 
 
+def attention_prefill_takes_chunks(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether `attention_prefill` would run the kernel that knows the chunk mask (bfloat16, heads of 64 or 128)."""
+    return bool(USE_TENSOR_CORE_PREFILL and USE_TCGEN05_PREFILL and dtype in _DTYPE_CODE
+                and lib().mll_attn_prefill_tc5_supported(dtype_code(dtype), head_dim))
+
+
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                       block_table, out, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                      window: int, scale: float, wide_tiles=None) -> None:
+                      window: int, scale: float, wide_tiles=None, chunk: int = 0) -> None:
     """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache.
     `wide_tiles`: (sequence, first row) int32 lists of the same rows in tiles of 128, which the tcgen05 kernel
-    works on; without them it walks the 64-row list and every other block finds nothing to do."""
+    works on; without them it walks the 64-row list and every other block finds nothing to do.
+    `chunk` > 0 (the tcgen05 kernel only; ask `attention_prefill_takes_chunks` first): key j is visible from query i
+    only if j // chunk == i // chunk."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
     for name, t in (("seq_slot", seq_slot), ("seq_ctx", seq_ctx), ("seq_qstart", seq_qstart),
                     ("seq_qlen", seq_qlen), ("tile_seq", tile_seq), ("tile_row0", tile_row0)):
@@ -781,9 +795,11 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
                                           _ptr(block_table), _ptr(out), ctypes.c_int(q.shape[0]),
                                           ctypes.c_longlong(k_cache.shape[0]), ctypes.c_int(n_tiles),
                                           ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
-                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(window),
+                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(window), ctypes.c_int(chunk),
                                           ctypes.c_float(scale), _stream()), "attention_prefill (tcgen05)")
         return
+    if chunk:
+        raise KernelError("attention prefill: only the tcgen05 kernel masks by chunks")
     if USE_TENSOR_CORE_PREFILL and lib().mll_attn_prefill_mma_supported(dtype_code(q.dtype), head_dim):
         _check(lib().mll_attn_prefill_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                           _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),

@@ -93,13 +93,24 @@ struct DeltaPrepArgs {
   float unit_eps;
 };
 
-// grid (tokens, 2 G + H), 128 threads: a block owns one head of one token - a q head, a k head, or a value head
-// together with that head's beta and decays.  Dynamic shared memory: max(d, dv) floats.
+// grid (token groups, 2 G + H), 128 threads: a block owns one head of `per_block` consecutive tokens - a q head, a
+// k head, or a value head together with that head's beta and decays.  Dynamic shared memory: max(d, dv) floats.
 template <typename T>
-__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepArgs a) {
+__device__ __forceinline__ void delta_prepare_token(const DeltaPrepArgs& a, int t, int unit, float* conv_out, float* scratch);
+
+template <typename T>
+__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepArgs a, int n_tokens, int per_block) {
   extern __shared__ float conv_out[];
   __shared__ float scratch[32];
-  const int t = blockIdx.x, unit = blockIdx.y;
+  const int t_end = min(n_tokens, (int)(blockIdx.x + 1) * per_block);
+  for (int t = blockIdx.x * per_block; t < t_end; ++t) {
+    delta_prepare_token<T>(a, t, blockIdx.y, conv_out, scratch);
+    __syncthreads();  // conv_out and scratch are free for the next token
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void delta_prepare_token(const DeltaPrepArgs& a, int t, int unit, float* conv_out, float* scratch) {
   const int H = a.n_heads, G = a.n_kv_heads, d = a.d, dv = a.dv, taps = a.taps;
   const int nqk = G * d, C = 2 * nqk + H * dv;
   const int seq = a.tok_seq[t];
@@ -276,11 +287,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     const float* v_s = stage + st * per_stage + TS * DP * (DELTA ? 3 : 2);
     const float* b_s = v_s + TS * CPB;
     for (int tt = 0; tt < nt; ++tt) {
-      const float* qv = q_s + tt * DP + r * ROWS;
-      const float* kv = k_s + tt * DP + r * ROWS;
+      // this lane's rows of q, k and g as 16-byte words (ROWS and DP are multiples of 4)
+      float qv[ROWS], kv[ROWS], gv[DELTA ? ROWS : 1];
+#pragma unroll
+      for (int i = 0; i < ROWS; i += 4) {
+        *reinterpret_cast<float4*>(qv + i) = *reinterpret_cast<const float4*>(q_s + tt * DP + r * ROWS + i);
+        *reinterpret_cast<float4*>(kv + i) = *reinterpret_cast<const float4*>(k_s + tt * DP + r * ROWS + i);
+        if (DELTA) *reinterpret_cast<float4*>(gv + i) = *reinterpret_cast<const float4*>(g_s + tt * DP + r * ROWS + i);
+      }
       float u = live ? v_s[tt * CPB + warp * CPW + cw] : 0.f;
       if (DELTA) {
-        const float* gv = g_s + tt * DP + r * ROWS;
         float p4[4] = {0.f, 0.f, 0.f, 0.f};  // four sums side by side: the chain of additions is a quarter as long
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
@@ -318,9 +334,16 @@ template <int ROWS, int R, bool DELTA>
 int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
   ScanArgs a = args;
   constexpr int DP = ROWS * R, CPB = (32 / R) * (SCAN_THREADS / 32);
-  a.tok_stage = DP <= 64 ? 16 : (DP <= 128 ? 8 : (DP <= 256 ? 4 : (DP <= 512 ? 2 : 1)));
+  a.tok_stage = DP <= 128 ? 16 : (DP <= 256 ? 8 : (DP <= 512 ? 4 : 2));
   const size_t smem = (size_t)2 * ((a.tok_stage * DP * (DELTA ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
   const dim3 grid((a.dv + CPB - 1) / CPB, a.n_heads, n_seqs);
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(state_scan_kernel<ROWS, R, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+      mll_set_error("state scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+      return (int)err;
+    }
+  }
   MLL_LAUNCH((state_scan_kernel<ROWS, R, DELTA>), grid, SCAN_THREADS, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
@@ -406,11 +429,13 @@ MLL_API int mll_delta_prepare(const void* proj, const float* rate, const float* 
   mll::DeltaPrepArgs a{proj, rate, conv_w, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, v, g, beta,
                        ld, rate_ld, n_heads, n_kv_heads, d, dv, taps, unit_eps};
   const size_t smem = (size_t)(d > dv ? d : dv) * sizeof(float);
-  const dim3 grid(n_tokens, 2 * n_kv_heads + n_heads);
+  // a prompt's thousands of tokens: several to a block, so that the launch is not a queue of tiny blocks
+  const int per_block = n_tokens >= 1024 ? 8 : 1;
+  const dim3 grid((n_tokens + per_block - 1) / per_block, 2 * n_kv_heads + n_heads);
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::delta_prepare_kernel<float>), grid, 128, smem, stream, a);
+    MLL_LAUNCH((mll::delta_prepare_kernel<float>), grid, 128, smem, stream, a, n_tokens, per_block);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), grid, 128, smem, stream, a);
+    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), grid, 128, smem, stream, a, n_tokens, per_block);
   else
     MLL_REQUIRE(false, "delta prepare: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

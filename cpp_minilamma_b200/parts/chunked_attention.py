@@ -105,10 +105,17 @@ class ChunkedAttention(Mixer):
         if shape.all_decode:
             return {}
         lists = {"tile_seq": [], "tile_row0": []}
+        wide = []
         for i in sorted(range(shape.n_seqs), key=lambda i: -shape.lens[i]):
             for row0 in range(0, shape.lens[i], K.PREFILL_TILE):
                 lists["tile_seq"].append(i)
                 lists["tile_row0"].append(row0)
+            for row0 in range(0, shape.lens[i], 2 * K.PREFILL_TILE):
+                wide.append((shape.starts[i] + min(shape.lens[i], row0 + 2 * K.PREFILL_TILE), i, row0))
+        # the same rows in tiles of twice as many, for the tcgen05 kernel, which walks its list from the back
+        wide.sort()
+        lists["wide_seq"] = [i for _, i, _ in wide]
+        lists["wide_row0"] = [row0 for _, _, row0 in wide]
         return lists
 
     def forward(self, step, h, cache):
@@ -125,7 +132,23 @@ class ChunkedAttention(Mixer):
                                   bool(self.position.interleaved) if self.position is not None else False,
                                   float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
         out = step.ws.buffer("attn", (T, self.n_heads * self.dv), act)
+        if (step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+                and not (self.chunk and self.window) and act == torch.bfloat16):
+            # single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed or
+            # mma.sync), which take the chunk as the key range's start; one block per (sequence, kv head)
+            K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, None, out,
+                               step.n_seqs, self.n_heads, self.n_kv_heads, self.d, 1, self.window, self.scale,
+                               chunk=self.chunk)
+            return self.o.forward(step, out, "o")
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
+        if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
+            # keys and values of one head size that the Llama attention's tcgen05 prompt kernel takes: that kernel,
+            # which knows the chunk mask too
+            K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
+                                tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out,
+                                tiles["tile_seq"].shape[0], self.n_heads, self.n_kv_heads, self.d, self.window,
+                                self.scale, wide_tiles=(tiles["wide_seq"], tiles["wide_row0"]), chunk=self.chunk)
+            return self.o.forward(step, out, "o")
         if tiles and self._tensor_cores():
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out, self.n_heads,

@@ -326,3 +326,83 @@ def test_state_scan_against_the_recurrence_written_out(delta, n_seqs, H, G, d, d
     scale = max(1.0, want_o.abs().max().item())
     assert (out.cpu().double() - want_o).abs().max().item() <= 2e-5 * scale
     assert (state_dev.cpu().double() - want_s).abs().max().item() <= 2e-5 * max(1.0, want_s.abs().max().item())
+
+
+@pytest.mark.parametrize("d,chunk,window", [(64, 48, 0), (128, 200, 0), (128, 64, 0), (64, 1000, 0), (128, 100, 30)])
+def test_tcgen05_prompt_kernel_with_chunks_against_the_general_one(d, chunk, window):
+    """Keys and values of one head size (64 or 128): chunked prompts run on the Llama attention's tcgen05 kernel.
+    Sequences start inside chunks and pages; tiles of 128 rows span several chunks."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    if not K.attention_prefill_takes_chunks(torch.bfloat16, d):
+        pytest.skip("the tcgen05 prompt kernel is switched off")
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(d + chunk)
+    H, G, n_pages = 4, 2, 24
+    starts, lens = [0, 70, 129], [300, 200, 1]
+    k_cache = (torch.randn((n_pages, G, PAGE, d), generator=gen) * 0.5).to(torch.bfloat16).to(dev)
+    v_cache = torch.randn((n_pages, G, PAGE, d), generator=gen).to(torch.bfloat16).to(dev)
+    order = torch.randperm(n_pages, generator=gen).tolist()
+    table = torch.full((3, 8), -1, dtype=torch.int32)
+    at = 0
+    for s, (start, n) in enumerate(zip(starts, lens)):
+        blocks = -(-(start + n) // PAGE)
+        table[s, :blocks] = torch.tensor(order[at:at + blocks], dtype=torch.int32)
+        at += blocks
+    table = table.to(dev)
+    T = sum(lens)
+    q = torch.randn((T, H * d), generator=gen).to(torch.bfloat16).to(dev)
+    narrow = [(s, r) for s, n in enumerate(lens) for r in range(0, n, K.PREFILL_TILE)]
+    wide = sorted((starts[s] + min(n, r + 128), s, r) for s, n in enumerate(lens) for r in range(0, n, 128))
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=dev)
+    state = make_step_state(dev, [0, 1, 2], starts, lens)
+    fast = torch.zeros((T, H * d), dtype=torch.bfloat16, device=dev)
+    plain = torch.zeros_like(fast)
+    scale = 1.0 / d ** 0.5
+    K.attention_prefill(q, k_cache, v_cache, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
+                        ints([s for s, _ in narrow]), ints([r for _, r in narrow]), table, fast, len(narrow), H, G, d,
+                        window, scale, wide_tiles=(ints([s for _, s, _ in wide]), ints([r for _, _, r in wide])),
+                        chunk=chunk)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, plain, H, G, d, d,
+                      chunk, window, scale)
+    torch.cuda.synchronize()
+    assert K.take_device_error() == 0
+    err = (fast.float() - plain.float()).abs()
+    assert torch.isfinite(fast.float()).all()
+    assert err.max().item() <= 0.03 * plain.float().abs().max().item(), (err.max().item(), int(err.argmax()) // (H * d))
+
+
+@pytest.mark.parametrize("d,chunk", [(64, 48), (128, 200), (128, 64), (32, 100), (96, 7), (64, 1000)])
+def test_decode_kernels_with_chunks_against_the_general_one(d, chunk):
+    """Single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed at 64 and
+    128, mma.sync otherwise) take the chunk as the start of the key range.  Contexts end just before, at and
+    just after chunk and page borders."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(d * 3 + chunk)
+    H, G, n_pages = 4, 2, 40
+    ctxs = sorted({1, 2, chunk, chunk + 1, 2 * chunk - 1, 2 * chunk, 2 * chunk + 1, 63, 64, 65, 128, 129, 300})
+    ctxs = [c for c in ctxs if c <= 320]
+    n = len(ctxs)
+    k_cache = (torch.randn((n_pages, G, PAGE, d), generator=gen) * 0.5).to(torch.bfloat16).to(dev)
+    v_cache = torch.randn((n_pages, G, PAGE, d), generator=gen).to(torch.bfloat16).to(dev)
+    table = torch.full((n, 8), -1, dtype=torch.int32)
+    for s, c in enumerate(ctxs):
+        blocks = -(-c // PAGE)
+        table[s, :blocks] = torch.randint(0, n_pages, (blocks,), generator=gen, dtype=torch.int32)  # reading only: pages may repeat
+    table = table.to(dev)
+    q = torch.randn((n, H * d), generator=gen).to(torch.bfloat16).to(dev)
+    state = make_step_state(dev, list(range(n)), [c - 1 for c in ctxs], [1] * n)
+    fast = torch.zeros((n, H * d), dtype=torch.bfloat16, device=dev)
+    plain = torch.zeros_like(fast)
+    scale = 1.0 / d ** 0.5
+    K.attention_decode(q, k_cache, v_cache, state.seq_slot, state.seq_ctx, table, None, fast, n, H, G, d, 1, 0, scale,
+                       chunk=chunk)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, plain, H, G, d, d,
+                      chunk, 0, scale)
+    torch.cuda.synchronize()
+    assert K.take_device_error() == 0
+    err = (fast.float() - plain.float()).abs().max(dim=1).values
+    assert torch.isfinite(fast.float()).all()
+    assert err.max().item() <= 0.03 * plain.float().abs().max().item(), (err.tolist(), ctxs)
