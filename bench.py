@@ -470,13 +470,15 @@ def design_rooflines(size, tokens, batch, context, peaks):
     seen = sum(min(i % C, i) + 1 for i in range(tokens))              # keys each prompt token sees in its chunk
     causal = tokens * (tokens + 1) // 2
     out["kupirax", "prefill", "local_attention_mma"] = ("tensor", 2.0 * H * seen * (d + dv))
-    out["llama", "prefill", "attention_prefill (tcgen05)"] = ("tensor", 2.0 * H * causal * 2 * d)
+    out["kupirax", "prefill", "attention_prefill"] = ("tensor", 2.0 * H * seen * (d + dv))
+    out["llama", "prefill", "attention_prefill"] = ("tensor", 2.0 * H * causal * 2 * d)
     qkv = (H * d + G * d + G * dv) * 2
     out["kupirax", "prefill", "local_attention_prepare"] = ("hbm", tokens * (2 * qkv))
     out["llama", "prefill", "rope_cache_write"] = ("hbm", tokens * (2 * qkv))
     out["kupirax", "decode", "local_attention_prepare"] = ("hbm", batch * (2 * qkv))
     visible = min(context % C, context) + 1
     out["kupirax", "decode", "local_attention"] = ("hbm", batch * visible * G * (d + dv) * 2)
+    out["kupirax", "decode", "attention_decode"] = ("hbm", batch * visible * G * (d + dv) * 2)
     out["llama", "decode", "attention_decode"] = ("hbm", batch * context * G * 2 * d * 2)
     # state mixers: what a step must move at least - the float32 inputs and outputs of the recurrence per token,
     # and in a decode step the state once in and once out
@@ -546,7 +548,7 @@ def bench_design(args):
             for (m, kind, name), (bound, amount) in expected.items():
                 if m != model:
                     continue
-                for key in [k for k in table if k.startswith(f"{kind}: {name}")]:
+                for key in [k for k in table if k == f"{kind}: {name}" or k.startswith(f"{kind}: {name} (")]:
                     us = table[key]["us_per_call"]
                     peak = peaks["hbm_gbs"] * 1e9 if bound == "hbm" else peaks["bf16_tflops"] * 1e12
                     table[key].update(bound=bound, frac=round(amount / (us * 1e-6) / peak, 4))

@@ -93,25 +93,17 @@ struct DeltaPrepArgs {
   float unit_eps;
 };
 
-// grid (token groups, 2 G + H), 128 threads: a block owns one head of `per_block` consecutive tokens - a q head, a
-// k head, or a value head together with that head's beta and decays.  Dynamic shared memory: max(d, dv) floats.
+// grid (ceil(tokens / 4), 2 G + H), 128 threads: a warp owns one head of one token - a q head, a k head, or a
+// value head together with that head's beta and decays - so that nothing waits on a block-wide barrier and a
+// multiprocessor has many independent chains of loads in flight.  Dynamic shared memory: 4 * max(d, dv) floats.
 template <typename T>
-__device__ __forceinline__ void delta_prepare_token(const DeltaPrepArgs& a, int t, int unit, float* conv_out, float* scratch);
-
-template <typename T>
-__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepArgs a, int n_tokens, int per_block) {
-  extern __shared__ float conv_out[];
-  __shared__ float scratch[32];
-  const int t_end = min(n_tokens, (int)(blockIdx.x + 1) * per_block);
-  for (int t = blockIdx.x * per_block; t < t_end; ++t) {
-    delta_prepare_token<T>(a, t, blockIdx.y, conv_out, scratch);
-    __syncthreads();  // conv_out and scratch are free for the next token
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ void delta_prepare_token(const DeltaPrepArgs& a, int t, int unit, float* conv_out, float* scratch) {
+__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepArgs a, int n_tokens) {
+  extern __shared__ float conv_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp, unit = blockIdx.y;
+  if (t >= n_tokens) return;  // whole warps leave; nothing below synchronises the block
   const int H = a.n_heads, G = a.n_kv_heads, d = a.d, dv = a.dv, taps = a.taps;
+  float* conv_out = conv_all + warp * max(d, dv);
   const int nqk = G * d, C = 2 * nqk + H * dv;
   const int seq = a.tok_seq[t];
   const int local = t - a.seq_qstart[seq];  // index among this step's tokens of the sequence
@@ -121,7 +113,7 @@ __device__ __forceinline__ void delta_prepare_token(const DeltaPrepArgs& a, int 
   const int width = is_v ? dv : d;
   const int c0 = is_v ? 2 * nqk + (unit - 2 * G) * dv : unit * d;  // first channel of the head
   float ss = 0.f;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+  for (int e = lane; e < width; e += 32) {
     const int c = c0 + e;
     float y = 0.f;
     for (int back = 0; back < taps; ++back) {  // the input `back` tokens ago meets tap taps - 1 - back
@@ -138,21 +130,20 @@ __device__ __forceinline__ void delta_prepare_token(const DeltaPrepArgs& a, int 
   }
   if (is_v) {
     const int h = unit - 2 * G;
-    __syncthreads();
-    for (int e = threadIdx.x; e < dv; e += blockDim.x) a.v[((size_t)t * H + h) * dv + e] = conv_out[e];
-    if (threadIdx.x == 0) a.beta[(size_t)t * H + h] = sigmoid_f(to_float(proj[(size_t)t * a.ld + C + h]));
+    for (int e = lane; e < dv; e += 32) a.v[((size_t)t * H + h) * dv + e] = conv_out[e];
+    if (lane == 0) a.beta[(size_t)t * H + h] = sigmoid_f(to_float(proj[(size_t)t * a.ld + C + h]));
     const float rate = expf(a.a_log[h]);
-    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+    for (int e = lane; e < d; e += 32) {
       const float sp = softplus_f(a.rate[(size_t)t * a.rate_ld + h * d + e] + a.dt_bias[h * d + e]);
       a.g[((size_t)t * H + h) * d + e] = expf(-rate * sp);
     }
     return;
   }
-  ss = block_sum(ss, scratch);  // q and k heads: unit length (and q / sqrt(d))
+  ss = warp_sum(ss);  // q and k heads: unit length (and q / sqrt(d))
   const bool is_q = unit < G;
   const float f = (is_q ? rsqrtf((float)d) : 1.f) / sqrtf(ss + a.unit_eps);
   float* dst = (is_q ? a.q : a.k) + ((size_t)t * G + (is_q ? unit : unit - G)) * d;
-  for (int e = threadIdx.x; e < d; e += blockDim.x) dst[e] = conv_out[e] * f;
+  for (int e = lane; e < d; e += 32) dst[e] = conv_out[e] * f;
 }
 
 // grid (ceil(C / 128), sequences): new state = the last taps - 1 of (old state, this step's inputs)
@@ -424,18 +415,16 @@ MLL_API int mll_delta_prepare(const void* proj, const float* rate, const float* 
   MLL_REQUIRE(d > 0 && dv > 0 && taps >= 1, "delta prepare: bad sizes");
   const int C = 2 * n_kv_heads * d + n_heads * dv;
   MLL_REQUIRE(ld >= C + n_heads && rate_ld >= n_heads * d, "delta prepare: row strides %d / %d too short", ld, rate_ld);
-  MLL_REQUIRE(d <= 8192 && dv <= 8192 && 2 * n_kv_heads + n_heads <= 65535, "delta prepare: heads too large or too many");
+  MLL_REQUIRE(d <= 2048 && dv <= 2048 && 2 * n_kv_heads + n_heads <= 65535, "delta prepare: heads too large or too many");
   if (n_tokens == 0) return 0;
   mll::DeltaPrepArgs a{proj, rate, conv_w, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, v, g, beta,
                        ld, rate_ld, n_heads, n_kv_heads, d, dv, taps, unit_eps};
-  const size_t smem = (size_t)(d > dv ? d : dv) * sizeof(float);
-  // a prompt's thousands of tokens: several to a block, so that the launch is not a queue of tiny blocks
-  const int per_block = n_tokens >= 1024 ? 8 : 1;
-  const dim3 grid((n_tokens + per_block - 1) / per_block, 2 * n_kv_heads + n_heads);
+  const size_t smem = (size_t)4 * (d > dv ? d : dv) * sizeof(float);
+  const dim3 grid((n_tokens + 3) / 4, 2 * n_kv_heads + n_heads);
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::delta_prepare_kernel<float>), grid, 128, smem, stream, a, n_tokens, per_block);
+    MLL_LAUNCH((mll::delta_prepare_kernel<float>), grid, 128, smem, stream, a, n_tokens);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), grid, 128, smem, stream, a, n_tokens, per_block);
+    MLL_LAUNCH((mll::delta_prepare_kernel<__nv_bfloat16>), grid, 128, smem, stream, a, n_tokens);
   else
     MLL_REQUIRE(false, "delta prepare: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
