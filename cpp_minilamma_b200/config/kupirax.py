@@ -84,12 +84,12 @@ class KupiraxLayer:
         if kind not in MIXER_TYPES:
             raise ConfigError(f"config.json: {what}.type {kind!r} is not one of {', '.join(MIXER_TYPES)}")
         m = _object(raw.get("mixer"), what + ".mixer")
-        layer = cls(type=kind, heads=take_int(m, "heads", minimum=1), dim=take_int(m, "dim", minimum=1),
-                    vdim=take_int(m, "vdim", minimum=1))
+        heads, dim = take_int(m, "heads", minimum=1), take_int(m, "dim", minimum=1)
+        layer = cls(type=kind, heads=heads, dim=dim, vdim=take_int(m, "vdim", default=dim, minimum=1))
         if kind == "attention":
-            layer.kv_heads = take_int(m, "kv_heads", minimum=1)
+            layer.kv_heads = take_int(m, "kv_heads", default=heads, minimum=1)
             layer.rot = Rotation.from_dict(m.get("rot"), what + ".mixer.rot")
-            layer.scale = take_float(m, "scale")
+            layer.scale = take_float(m, "scale", default=dim ** -0.5)
             if m.get("mask") is not None:
                 layer.chunk = take_int(_object(m["mask"], what + ".mixer.mask"), "size", minimum=1)
         elif kind == "retention":
@@ -100,7 +100,7 @@ class KupiraxLayer:
                 raise ConfigError(f"config.json: {what}.mixer.decay must list one number per head")
             layer.decay = [float(x) for x in decay]
         else:
-            layer.kv_heads = take_int(m, "kv_heads", minimum=1)
+            layer.kv_heads = take_int(m, "kv_heads", default=heads, minimum=1)
             layer.conv = take_int(m, "conv", minimum=1)
             layer.decay_rank = take_int(m, "decay_rank", default=0, minimum=0)
             layer.gate_rank = take_int(m, "gate_rank", default=0, minimum=0)

@@ -68,7 +68,8 @@ def run_alone(llm, toks, cuts):
     return np.concatenate(rows)
 
 
-LENGTH = {"attention_only": 75, "retention_only": 140, "delta_only": 75, "mixed": 135, "ones": 200, "wide": 70}
+LENGTH = {"attention_only": 75, "retention_only": 140, "delta_only": 75, "mixed": 135, "ones": 200, "wide": 70,
+          "odd": 90}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -81,7 +82,7 @@ def test_whole_prompt(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["attention_only", "retention_only", "delta_only", "mixed", "ones"])
+@pytest.mark.parametrize("name", ["attention_only", "retention_only", "delta_only", "mixed", "ones", "odd"])
 def test_prompt_then_token_by_token(models, name, dtype):
     """A short prompt, then a long run of single tokens through cache and state: over chunk borders (every 5, 8,
     64 or 96 tokens), over the page border, with keys both just inside and just outside the chunk at every step."""

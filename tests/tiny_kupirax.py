@@ -62,6 +62,11 @@ CONFIGS = {
                             retention(heads=2, dim=136, vdim=48, decay=(0.75, 0.9990234375), rot_dims=64, ff=0),
                             attention(heads=2, kv_heads=1, dim=72, vdim=136, chunk=16, rot_dims=36, ff=0)],
                            width=64, vocab=50),
+    # nothing divisible by four: a width of 50, heads of 6 and 10, the kernels' scalar paths
+    "odd": lambda: config([channel_delta(heads=3, kv_heads=1, dim=6, vdim=10, conv=3, ff=30),
+                           attention(heads=3, kv_heads=1, dim=6, vdim=10, chunk=11, rot_dims=2, ff=0),
+                           retention(heads=2, dim=10, vdim=6, decay=(0.875, 0.9921875), rot_dims=6, ff=30)],
+                          width=50, vocab=53, loop=(0, 3, 2)),
 }
 RANKS = (5, 7)  # inner sizes of the delta layers' two low-rank pairs (the configuration does not give them)
 
