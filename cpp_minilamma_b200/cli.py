@@ -94,7 +94,7 @@ def inspect(folder: str) -> None:
     config = load_config(folder)
     print(f"architecture: {config.architecture}")
     for key, value in config.to_dict().items():
-        if key != "architectures":
+        if key not in ("architectures", "architecture"):
             print(f"{key}: {json.dumps(value)}")
     model = build_model(config, "float32", "cpu", max_positions=1)
     print(f"parameters: {model.parameter_count()}")

@@ -115,3 +115,23 @@ def test_tensor_list_matches_the_folder(tmp_path):
             assert all(a == -1 or a == b for a, b in zip(shape, shapes[n])), n
         needs = model.cache_needs()
         assert len(needs) == len(pk.schedule(cfg))  # every run of a looped layer has a cache or state of its own
+
+
+def test_command_line_writes_and_inspects_a_random_folder(tmp_path, capsys):
+    """`random` needs the sizes that only tensors give (the low-rank pairs' inner sizes) named in the configuration."""
+    import json
+    from cpp_minilamma_b200.cli import main
+    cfg = tk.CONFIGS["mixed"]()
+    (tmp_path / "c.json").write_text(json.dumps(cfg))
+    assert main(["random", str(tmp_path / "m"), "--config", str(tmp_path / "c.json")]) == 1
+    assert "configuration must name it" in capsys.readouterr().err
+    for layer in cfg["layers"]:
+        if layer["type"] == "channel_delta":
+            layer["mixer"]["decay_rank"], layer["mixer"]["gate_rank"] = tk.RANKS
+    (tmp_path / "c.json").write_text(json.dumps(cfg))
+    assert main(["random", str(tmp_path / "m"), "--config", str(tmp_path / "c.json"), "--seed", "3"]) == 0
+    assert main(["inspect", str(tmp_path / "m")]) == 0
+    out = capsys.readouterr().out
+    assert "architecture: Kupirax" in out and "tensor l4.mix.q.conv [16, 5] bfloat16" in out and "status=ok" in out
+    model = ml.build_model(ml.load_config(tmp_path / "m"), "float32", "cpu", max_positions=8)
+    assert {s.name for s in model.weight_specs()} == set(tk.tensor_shapes(cfg))
