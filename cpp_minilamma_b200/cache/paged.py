@@ -113,7 +113,9 @@ class CacheGroup:
         # one page and one block-table row beyond those that are handed out: the padding slot's (SequenceCache.pad_slot)
         shape = (len(entries), n_pages + 1, need.n_kv_heads, PAGE, need.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty((*shape[:-1], need.v_head_dim or need.head_dim), dtype=dtype, device=device)
+        # values that are the keys' leading columns have no storage of their own
+        self.v = self.k if need.v_in_k else torch.empty((*shape[:-1], need.v_head_dim or need.head_dim), dtype=dtype,
+                                                        device=device)
         self.table_host = np.full((n_slots + 1, max_blocks), -1, dtype=np.int32)
         self.table_host[n_slots, 0] = n_pages
         self.table_dev = torch.from_numpy(self.table_host.copy()).to(device)
@@ -356,7 +358,8 @@ class SequenceCache:
 
     def kv_bytes_per_token(self) -> int:
         width = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * g.need.n_kv_heads * (g.need.head_dim + (g.need.v_head_dim or g.need.head_dim)) * width
+        return sum(len(g.entries) * g.need.n_kv_heads *
+                   (g.need.head_dim + (0 if g.need.v_in_k else (g.need.v_head_dim or g.need.head_dim))) * width
                    for g in self.groups)
 
     def read_kv(self, entry: int, slot: int, length: Optional[int] = None):

@@ -3,7 +3,11 @@
 // encoding of the first `rot` dimensions of a head only, and a mask that is causal inside chunks:
 // query i sees key j iff j <= i and j / chunk == i / chunk (chunk 0: every earlier key), and with a
 // window w > 0 only keys j > i - w.  Chunks count from position 0 of the sequence, whatever portion of it
-// a step brings.
+// a step brings.  Two further options: a query temperature (q at position p is multiplied by
+// 1 + coef * ln(floor((p + 1) / every) + 1) before it is stored) and a sink in the softmax (one more term
+// exp(0) in the denominator that carries no value, so a row's weights may sum to less than one).  The values
+// may be the leading dv columns of the key rows (v_ld = d: a layer that caches one latent row per position and
+// reads it as key and as value); otherwise they have pages of their own (v_ld = dv).
 //
 // Two kernels, for prompts and single tokens alike:
 //   * prepare: one block per token.  q and k are each divided by the root mean square of their whole
@@ -32,6 +36,8 @@ struct LocalPrepArgs {
   void* v_cache;          // [pages, Hk, PAGE, dv]
   int ld, n_heads, n_kv_heads, d, dv, rot, interleaved, max_blocks;
   float eps;
+  float q_temp_coef;      // query temperature: 0 and 0 for none
+  int q_temp_every;
 };
 
 template <typename T>
@@ -57,6 +63,7 @@ __global__ void __launch_bounds__(256) local_prepare_kernel(LocalPrepArgs a) {
     fk = 1.f / sqrtf(sk / (float)nk + a.eps);
   }
   const int pos = a.tok_pos[t];
+  if (a.q_temp_every > 0) fq *= 1.f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every) + 1.f);
   const int slot = a.seq_slot[a.tok_seq[t]];
   const int page = a.block_table[(size_t)slot * a.max_blocks + pos / MLL_PAGE];
   const int in_page = pos % MLL_PAGE;
@@ -130,6 +137,8 @@ struct LocalAttnArgs {
   void* out;             // [T, Hq * dv]
   int n_tokens, n_heads, n_kv_heads, d, dv, chunk, window, max_blocks;
   float scale;
+  int sink;              // 1: the softmax's denominator has one more term exp(0)
+  int v_ld;              // elements between value rows: dv, or d when the values are the keys' leading columns
 };
 
 // grid (tokens, Hk * head chunks), 128 threads.  A block owns one token, one kv head and up to `hpb` of the
@@ -173,8 +182,8 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
     q_s[g * d_pad + e] = to_float(((const T*)a.q)[((size_t)t * a.n_heads + h0 + g) * d + e]) * a.scale;
   }
   for (int i = tid; i < ng; i += 128) {
-    m_s[i] = -INFINITY;
-    l_s[i] = 0.f;
+    m_s[i] = a.sink ? 0.f : -INFINITY;  // the sink: a key that scores 0 and has no value, seen before all others
+    l_s[i] = a.sink ? 1.f : 0.f;
   }
   float acc[NACC];
 #pragma unroll
@@ -184,7 +193,7 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
   auto load_tiles = [&](int page_index, int stage) {
     const int page = table[page_index];
     const T* kg = (const T*)a.k_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * d;
-    const T* vg = (const T*)a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * dv;
+    const T* vg = (const T*)a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * a.v_ld;
     T* kd = k_s + stage * k_tile;
     T* vd = v_s + stage * v_tile;
     const int r_lo = max(0, first - page_index * MLL_PAGE), r_hi = min(MLL_PAGE, pos + 1 - page_index * MLL_PAGE);
@@ -196,7 +205,7 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
       }
       for (int c = tid; c < (r_hi - r_lo) * vc; c += 128) {
         const int r = r_lo + c / vc, cc = c % vc;
-        cp_async16(vd + (size_t)r * v_stride + cc * PAD, vg + (size_t)r * dv + cc * PAD);
+        cp_async16(vd + (size_t)r * v_stride + cc * PAD, vg + (size_t)r * a.v_ld + cc * PAD);
       }
     } else {
       for (int c = tid; c < (r_hi - r_lo) * d; c += 128) {
@@ -205,7 +214,7 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
       }
       for (int c = tid; c < (r_hi - r_lo) * dv; c += 128) {
         const int r = r_lo + c / dv, e = c % dv;
-        vd[(size_t)r * v_stride + e] = vg[(size_t)r * dv + e];
+        vd[(size_t)r * v_stride + e] = vg[(size_t)r * a.v_ld + e];
       }
     }
   };
@@ -297,7 +306,7 @@ int launch_local_attention(const LocalAttnArgs& a, cudaStream_t stream) {
   const int group = a.n_heads / a.n_kv_heads;
   const int hpb = max(1, min(group, 1024 / a.dv));       // at most 8 accumulators a thread
   const int chunks = (group + hpb - 1) / hpb;
-  const int vec = (a.d % PAD == 0 && a.dv % PAD == 0) ? 1 : 0;
+  const int vec = (a.d % PAD == 0 && a.dv % PAD == 0 && a.v_ld % PAD == 0) ? 1 : 0;
   const int k_stride = ((a.d + PAD - 1) / PAD) * PAD + PAD, v_stride = ((a.dv + PAD - 1) / PAD) * PAD;
   size_t fixed = (size_t)(hpb * ((a.d + 3) & ~3) + hpb * MLL_PAGE + 3 * hpb) * sizeof(float);
   fixed = (fixed + 15) & ~(size_t)15;
@@ -337,15 +346,16 @@ MLL_API int mll_local_attention_prepare(const void* qkv, const float* q_weight, 
                                         const int* tok_seq, const int* seq_slot, const int* block_table, void* q_out,
                                         void* k_cache, void* v_cache, int dtype, int n_tokens, int ld, int n_heads,
                                         int n_kv_heads, int d, int dv, int rot, int interleaved, int max_blocks,
-                                        float eps, cudaStream_t stream) {
+                                        float eps, float q_temp_coef, int q_temp_every, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && d > 0 && dv > 0, "local attention prepare: bad sizes");
   MLL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "local attention prepare: %d rotated dimensions of %d", rot, d);
   MLL_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "local attention prepare: one norm weight without the other");
   MLL_REQUIRE(ld >= n_heads * d + n_kv_heads * (d + dv), "local attention prepare: row stride %d too short", ld);
+  MLL_REQUIRE(q_temp_every >= 0, "local attention prepare: negative temperature period");
   if (n_tokens == 0) return 0;
   mll::LocalPrepArgs a{qkv, q_weight, k_weight, rot > 0 ? cos_table : nullptr, sin_table, tok_pos, tok_seq, seq_slot,
                        block_table, q_out, k_cache, v_cache, ld, n_heads, n_kv_heads, d, dv, rot, interleaved,
-                       max_blocks, eps};
+                       max_blocks, eps, q_temp_coef, q_temp_every};
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::local_prepare_kernel<float>), n_tokens, 256, 0, stream, a);
   else if (dtype == MLL_BF16)
@@ -359,13 +369,14 @@ MLL_API int mll_local_attention_prepare(const void* qkv, const float* q_weight, 
 MLL_API int mll_local_attention(const void* q, const void* k_cache, const void* v_cache, const int* tok_pos,
                                 const int* tok_seq, const int* seq_slot, const int* block_table, void* out, int dtype,
                                 int n_tokens, int n_heads, int n_kv_heads, int d, int dv, int chunk, int window,
-                                int max_blocks, float scale, cudaStream_t stream) {
+                                int max_blocks, float scale, int sink, int v_in_k, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention: bad head counts");
   MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0 && dv <= 1024, "local attention: head sizes %d / %d (at most 1024)", d, dv);
   MLL_REQUIRE(chunk >= 0 && window >= 0, "local attention: negative chunk or window");
+  MLL_REQUIRE(!v_in_k || dv <= d, "local attention: values of %d cannot be the leading columns of keys of %d", dv, d);
   if (n_tokens == 0) return 0;
   mll::LocalAttnArgs a{q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_tokens, n_heads,
-                       n_kv_heads, d, dv, chunk, window, max_blocks, scale};
+                       n_kv_heads, d, dv, chunk, window, max_blocks, scale, sink ? 1 : 0, v_in_k ? d : dv};
   if (dtype == MLL_F32) return mll::launch_local_attention<float>(a, stream);
   if (dtype == MLL_BF16) return mll::launch_local_attention<__nv_bfloat16>(a, stream);
   MLL_REQUIRE(false, "local attention: unknown dtype %d", dtype);

@@ -23,6 +23,8 @@ struct LocalMmaArgs {
   __nv_bfloat16* out;            // [T, Hq * dv]
   int n_heads, n_kv_heads, max_blocks, window, chunk, d, dv;
   float scale_log2;
+  int sink;                      // 1: one more term exp(0) in the softmax's denominator, without a value
+  int v_ld;                      // elements between value rows: dv, or d when the values are the keys' leading columns
 };
 
 template <int DK, int DV>
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   auto load_page = [&](int page_index, int stage) {
     const int page = table[page_index];
     const __nv_bfloat16* kg = a.k_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * d;
-    const __nv_bfloat16* vg = a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * dv;
+    const __nv_bfloat16* vg = a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * a.v_ld;
     __nv_bfloat16* kd = kv_s + (size_t)stage * (L::KTILE + L::VTILE);
     __nv_bfloat16* vd = kd + L::KTILE;
     const int valid_rows = ctx - page_index * MLL_PAGE;  // rows past the cached length hold no data
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     for (int c = tid; c < MLL_PAGE * VCPR; c += 128) {
       const int r = c / VCPR, cc = c % VCPR;
       const bool in = cc * 8 < dv && r < valid_rows;
-      cp_async16_zfill(vd + r * L::VS + cc * 8, vg + (size_t)r * dv + (in ? cc * 8 : 0), in);
+      cp_async16_zfill(vd + r * L::VS + cc * 8, vg + (size_t)r * a.v_ld + (in ? cc * 8 : 0), in);
     }
   };
 
@@ -94,7 +96,8 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   for (int n = 0; n < NT_OUT; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // with a sink every row starts as if it had seen one key that scores 0 and has no value
+  float m_run[2] = {a.sink ? 0.f : -INFINITY, a.sink ? 0.f : -INFINITY}, l_run[2] = {a.sink ? 1.f : 0.f, a.sink ? 1.f : 0.f};
 
   for (int p = p_first; p <= p_last; ++p) {
     const int stage = (p - p_first) & 1;
@@ -245,15 +248,16 @@ MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const vo
                                     const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
                                     const int* tile_row0, const int* block_table, void* out, int n_tiles, int n_heads,
                                     int n_kv_heads, int d, int dv, int chunk, int window, int max_blocks, float scale,
-                                    cudaStream_t stream) {
+                                    int sink, int v_in_k, cudaStream_t stream) {
   MLL_REQUIRE(mll_local_attention_mma_supported(MLL_BF16, d, dv), "local attention (mma): head sizes %d / %d", d, dv);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention (mma): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_heads <= 65535 && chunk >= 0 && window >= 0, "local attention (mma): bad tile count, chunk or window");
+  MLL_REQUIRE(!v_in_k || dv <= d, "local attention (mma): values of %d cannot be the leading columns of keys of %d", dv, d);
   if (n_tiles == 0) return 0;
   mll::LocalMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                       seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, d, dv,
-                      scale * 1.4426950408889634f};
+                      scale * 1.4426950408889634f, sink ? 1 : 0, v_in_k ? d : dv};
   if (d <= 32) return mll::dispatch_local_mma_v<32>(a, n_tiles, stream);
   if (d <= 64) return mll::dispatch_local_mma_v<64>(a, n_tiles, stream);
   if (d <= 128) return mll::dispatch_local_mma_v<128>(a, n_tiles, stream);

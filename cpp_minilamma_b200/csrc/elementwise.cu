@@ -21,7 +21,7 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 29; }
+MLL_API int mll_abi_version() { return 30; }
 
 // Cache positions per page, for the Python side to check against its own constant.
 MLL_API int mll_page() { return MLL_PAGE; }
@@ -227,6 +227,43 @@ __global__ void gather_int32_kernel(int* __restrict__ dst, const int* __restrict
   dst[i] = at >= 0 && at < n_src ? src[at] : 0;
 }
 
+// out[t, 0:D] = x[t] + delta[t] (delta optional), out[t, D:2D] = x0[t]: the float32 residual stream (with the
+// output of the last part still to be added) beside an earlier state of it, as one row for the product that
+// mixes the two.  The sum is float32; T is the product's input type.
+template <typename T>
+__global__ void stream_concat_kernel(const float* __restrict__ x, const T* __restrict__ delta,
+                                     const float* __restrict__ x0, T* __restrict__ out, size_t total, int width) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / (2 * width);
+    const int c = (int)(i % (2 * width));
+    float v;
+    if (c < width) {
+      v = x[t * width + c];
+      if (delta) v += to_float(delta[t * width + c]);
+    } else {
+      v = x0[t * width + c - width];
+    }
+    out[i] = from_float<T>(v);
+  }
+}
+
+// out[t, h * dv + i] = in[t * in_t + h * in_h + i] * sigmoid(gate[t * gate_ld + (per_head ? h : h * dv + i)]):
+// the output gate of an attention layer, one number per head or one per element, read from the projection's
+// own row; the input may lie head-major (a batched product's result).  out may be in itself when the layouts agree.
+template <typename T>
+__global__ void heads_gate_kernel(const T* __restrict__ in, const T* __restrict__ gate, T* __restrict__ out,
+                                  size_t total, int n_heads, int dv, long long in_t, long long in_h, int gate_ld,
+                                  int per_head) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / ((size_t)n_heads * dv);
+    const int c = (int)(i % ((size_t)n_heads * dv));
+    const int h = c / dv, e = c % dv;
+    const float g = to_float(gate[t * gate_ld + (per_head ? h : c)]);
+    const float v = to_float(in[t * in_t + (size_t)h * in_h + e]);
+    out[i] = from_float<T>(v / (1.f + expf(-g)));
+  }
+}
+
 }  // namespace mll
 
 // dst: int32 [n]; src: int32 [n_src]; index: int32 [n].  dst and src must not overlap.
@@ -345,6 +382,47 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
     MLL_LAUNCH((mll::swiglu_kernel<__nv_bfloat16>), (int)blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
   else
     MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// x, x0: float32 [n_tokens, width]; delta: optional [n_tokens, width] of `dtype`; out: [n_tokens, 2 width] of `dtype`.
+MLL_API int mll_stream_concat(const float* x, const void* delta, const float* x0, void* out, int dtype, int n_tokens,
+                              int width, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && width > 0, "stream_concat: bad sizes tokens=%d width=%d", n_tokens, width);
+  if (n_tokens == 0) return 0;
+  const size_t total = (size_t)n_tokens * 2 * width;
+  long long blocks = (long long)((total + 255) / 256);
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::stream_concat_kernel<float>), (int)blocks, 256, 0, stream, x, (const float*)delta, x0, (float*)out,
+               total, width);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::stream_concat_kernel<__nv_bfloat16>), (int)blocks, 256, 0, stream, x, (const __nv_bfloat16*)delta,
+               x0, (__nv_bfloat16*)out, total, width);
+  else
+    MLL_REQUIRE(false, "stream_concat: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// in: element (t, h, i) at t * in_t + h * in_h + i; gate: [n_tokens, gate_ld] (already offset to the gate's first
+// column); out: [n_tokens, n_heads * dv]; all of `dtype`.
+MLL_API int mll_heads_gate(const void* in, const void* gate, void* out, int dtype, int n_tokens, int n_heads, int dv,
+                           long long in_t, long long in_h, int gate_ld, int per_head, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && dv > 0 && gate_ld > 0, "heads_gate: bad sizes");
+  if (n_tokens == 0) return 0;
+  const size_t total = (size_t)n_tokens * n_heads * dv;
+  long long blocks = (long long)((total + 255) / 256);
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::heads_gate_kernel<float>), (int)blocks, 256, 0, stream, (const float*)in, (const float*)gate,
+               (float*)out, total, n_heads, dv, in_t, in_h, gate_ld, per_head);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::heads_gate_kernel<__nv_bfloat16>), (int)blocks, 256, 0, stream, (const __nv_bfloat16*)in,
+               (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, total, n_heads, dv, in_t, in_h, gate_ld, per_head);
+  else
+    MLL_REQUIRE(false, "heads_gate: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
   return 0;
 }

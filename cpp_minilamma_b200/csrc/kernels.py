@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 29
+ABI_VERSION = 30
 MAX_TOP_K = 1024
 
 
@@ -491,6 +491,76 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
                                   ctypes.c_int(width), ctypes.c_float(eps), _stream()), "rmsnorm")
 
 
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                  out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """x += delta (float32 residual, in place); out = (x - mean) / sqrt(var + eps) * weight + bias, the variance
+    being the mean squared deviation.  `rows` as in `add_rmsnorm`."""
+    _need(x, "layernorm x", torch.float32, 2)
+    _need(weight, "layernorm weight", torch.float32, 1)
+    _need(out, "layernorm out", None, 2)
+    width = x.shape[1]
+    if weight.shape[0] != width or out.shape[1] != width:
+        raise KernelError(f"layernorm: widths differ: x {width}, weight {weight.shape[0]}, out {out.shape[1]}")
+    if bias is not None:
+        _need(bias, "layernorm bias", torch.float32, 1)
+        if bias.shape[0] != width:
+            raise KernelError(f"layernorm: bias of {bias.shape[0]}, expected {width}")
+    delta_dtype = out.dtype
+    if delta is not None:
+        _need(delta, "layernorm delta", None, 2)
+        delta_dtype = delta.dtype
+        if delta.shape != x.shape:
+            raise KernelError(f"layernorm: delta {tuple(delta.shape)} differs from x {tuple(x.shape)}")
+    if delta_dtype != out.dtype and not (delta_dtype == torch.bfloat16 and out.dtype == torch.float32):
+        raise KernelError(f"layernorm: delta {delta_dtype} with out {out.dtype}")
+    if rows is not None:
+        _need(rows, "layernorm rows", torch.int32, 1)
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if out.shape[0] != n_rows:
+        raise KernelError(f"layernorm: out has {out.shape[0]} rows, expected {n_rows}")
+    _check(lib().mll_add_layernorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(bias), _ptr(out), _ptr(rows),
+                                   dtype_code(delta_dtype), dtype_code(out.dtype), ctypes.c_int(n_rows),
+                                   ctypes.c_int(width), ctypes.c_float(eps), _stream()), "layernorm")
+
+
+def stream_concat(x: torch.Tensor, delta: Optional[torch.Tensor], x0: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [x[t] + delta[t] ; x0[t]] in out's dtype: the float32 stream (with a part's output still to be
+    added) beside an earlier state of it."""
+    _need(x, "stream_concat x", torch.float32, 2)
+    _need(x0, "stream_concat x0", torch.float32, 2)
+    _need(out, "stream_concat out", None, 2)
+    n, width = x.shape
+    if x0.shape != x.shape or tuple(out.shape) != (n, 2 * width):
+        raise KernelError(f"stream_concat: x {tuple(x.shape)}, x0 {tuple(x0.shape)}, out {tuple(out.shape)}")
+    if delta is not None:
+        _need(delta, "stream_concat delta", out.dtype, 2)
+        if delta.shape != x.shape:
+            raise KernelError("stream_concat: delta differs from x in shape")
+    _check(lib().mll_stream_concat(_ptr(x), _ptr(delta), _ptr(x0), _ptr(out), dtype_code(out.dtype), ctypes.c_int(n),
+                                   ctypes.c_int(width), _stream()), "stream_concat")
+
+
+def heads_gate(values: torch.Tensor, gate_rows: torch.Tensor, gate_col: int, out: torch.Tensor, n_heads: int, dv: int,
+               per_head: bool, head_major: bool = False) -> None:
+    """out[t, h * dv + i] = values(t, h, i) * sigmoid(gate_rows[t, gate_col + (h if per_head else h * dv + i)]).
+    values is [T, H * dv], or [H, T, dv] with `head_major`; out [T, H * dv] may be values itself in the first case."""
+    _need(values, "heads_gate values", None)
+    _need(gate_rows, "heads_gate gate", values.dtype, 2)
+    _need(out, "heads_gate out", values.dtype, 2)
+    n = out.shape[0]
+    if out.shape[1] != n_heads * dv or values.numel() != out.numel() or gate_rows.shape[0] != n:
+        raise KernelError(f"heads_gate: values {tuple(values.shape)}, out {tuple(out.shape)} for {n_heads} heads of {dv}")
+    if gate_col + (n_heads if per_head else n_heads * dv) > gate_rows.shape[1]:
+        raise KernelError("heads_gate: the gate's columns lie outside its rows")
+    if head_major and values.data_ptr() == out.data_ptr():
+        raise KernelError("heads_gate: a head-major input cannot be gated in place")
+    in_t, in_h = (dv, n * dv) if head_major else (n_heads * dv, dv)
+    gate = ctypes.c_void_p(gate_rows.data_ptr() + gate_col * gate_rows.element_size())
+    _check(lib().mll_heads_gate(_ptr(values), gate, _ptr(out), dtype_code(out.dtype), ctypes.c_int(n),
+                                ctypes.c_int(n_heads), ctypes.c_int(dv), ctypes.c_longlong(in_t), ctypes.c_longlong(in_h),
+                                ctypes.c_int(gate_rows.shape[1]), ctypes.c_int(int(per_head)), _stream()), "heads_gate")
+
+
 def apply_row_norm(values: torch.Tensor, row_norm: RowNorm, out: torch.Tensor) -> None:
     """out = values * the rows' norm factors (bfloat16 [T, D]): finishes a norm that the product behind it
     cannot finish itself."""
@@ -847,12 +917,16 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, requ
 # --------------------------------------------------------------------------- #
 def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out,
                             k_cache, v_cache, n_heads: int, n_kv_heads: int, d: int, dv: int, rot: int,
-                            interleaved: bool, eps: float) -> None:
+                            interleaved: bool, eps: float, q_temp=None) -> None:
     """qkv [T, ld] (q heads of d, k heads of d, v heads of dv): q and k each divided by the root mean square of
     their whole projection and multiplied by `q_weight` / `k_weight` (float32; both None: no norm), the first
     `rot` dimensions of every q and k head rotated, q to `q_out` [T, Hq * d], k and v into the cache pages
-    ([pages, Hk, PAGE, d] and [pages, Hk, PAGE, dv])."""
+    ([pages, Hk, PAGE, d] and [pages, Hk, PAGE, dv]).  `q_temp` = (coef, every): q at position p is also
+    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
     _need(qkv, "local attention qkv", None, 2)
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    if q_temp and every < 1:
+        raise KernelError(f"local attention: a query temperature every {every} positions")
     _need(q_out, "local attention q", qkv.dtype, 2)
     _need(k_cache, "local attention k cache", qkv.dtype, 4)
     _need(v_cache, "local attention v cache", qkv.dtype, 4)
@@ -880,13 +954,27 @@ def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq,
         _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(block_table), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
         dtype_code(qkv.dtype), ctypes.c_int(n), ctypes.c_int(qkv.shape[1]), ctypes.c_int(n_heads),
         ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(rot), ctypes.c_int(int(interleaved)),
-        ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), _stream()), "local_attention_prepare")
+        ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), ctypes.c_float(coef), ctypes.c_int(every), _stream()),
+        "local_attention_prepare")
+
+
+def _check_local_caches(k_cache, v_cache, n_kv_heads: int, d: int, dv: int, v_in_k: bool) -> None:
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, d):
+        raise KernelError(f"local attention: key cache {tuple(k_cache.shape)} does not fit {n_kv_heads} heads of {d}")
+    if v_in_k:
+        if v_cache.data_ptr() != k_cache.data_ptr() or dv > d:
+            raise KernelError("local attention: values inside the keys need the key cache itself and dv <= d")
+    elif tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, dv):
+        raise KernelError(f"local attention: value cache {tuple(v_cache.shape)} does not fit {n_kv_heads} heads of {dv}")
 
 
 def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_heads: int, n_kv_heads: int,
-                    d: int, dv: int, chunk: int, window: int, scale: float) -> None:
+                    d: int, dv: int, chunk: int, window: int, scale: float, sink: bool = False,
+                    v_in_k: bool = False) -> None:
     """out [T, Hq * dv] = softmax(scale * q . k) v over the keys j <= i of the query's own chunk (j // chunk ==
-    i // chunk; chunk 0: all) and window (j > i - window; 0: none); the step's own keys are in the cache already."""
+    i // chunk; chunk 0: all) and window (j > i - window; 0: none); the step's own keys are in the cache already.
+    `sink`: the softmax's denominator has one more term exp(0).  `v_in_k`: the values are the leading dv columns of
+    the key rows (v_cache is k_cache)."""
     _need(q, "local attention q", None, 2)
     _need(out, "local attention out", q.dtype, 2)
     _need(k_cache, "local attention k cache", q.dtype, 4)
@@ -894,13 +982,13 @@ def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table
     n = q.shape[0]
     if tuple(q.shape) != (n, n_heads * d) or tuple(out.shape) != (n, n_heads * dv):
         raise KernelError(f"local attention: q {tuple(q.shape)} / out {tuple(out.shape)} for {n_heads} heads of {d} / {dv}")
-    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, d) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, dv):
-        raise KernelError("local attention: the caches do not fit the head sizes")
+    _check_local_caches(k_cache, v_cache, n_kv_heads, d, dv, v_in_k)
     _check(lib().mll_local_attention(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(block_table),
         _ptr(out), dtype_code(q.dtype), ctypes.c_int(n), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk), ctypes.c_int(window),
-        ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), _stream()), "local_attention")
+        ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)), ctypes.c_int(int(v_in_k)),
+        _stream()), "local_attention")
 
 
 USE_TENSOR_CORE_LOCAL = True  # tests switch it off to reach the general kernel in bfloat16 prompt steps
@@ -913,7 +1001,7 @@ def local_attention_mma_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
 
 def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                           block_table, out, n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int,
-                          scale: float) -> None:
+                          scale: float, sink: bool = False, v_in_k: bool = False) -> None:
     """`local_attention` for prompt steps in bfloat16 on tensor cores: the work is a list of tiles of up to
     PREFILL_TILE query rows, (sequence, first row among the sequence's new tokens)."""
     _need(q, "local attention q", torch.bfloat16, 2)
@@ -923,8 +1011,7 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
     n = q.shape[0]
     if tuple(q.shape) != (n, n_heads * d) or tuple(out.shape) != (n, n_heads * dv):
         raise KernelError(f"local attention: q {tuple(q.shape)} / out {tuple(out.shape)} for {n_heads} heads of {d} / {dv}")
-    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, d) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, dv):
-        raise KernelError("local attention: the caches do not fit the head sizes")
+    _check_local_caches(k_cache, v_cache, n_kv_heads, d, dv, v_in_k)
     for name, t in (("tile_seq", tile_seq), ("tile_row0", tile_row0)):
         _need(t, f"local attention {name}", torch.int32, 1)
     if tile_seq.shape != tile_row0.shape:
@@ -933,8 +1020,8 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx), _ptr(seq_qstart), _ptr(seq_qlen),
         _ptr(tile_seq), _ptr(tile_row0), _ptr(block_table), _ptr(out), ctypes.c_int(tile_seq.shape[0]),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
-        ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), _stream()),
-        "local_attention_mma")
+        ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
+        ctypes.c_int(int(v_in_k)), _stream()), "local_attention_mma")
 
 
 # --------------------------------------------------------------------------- #
@@ -1059,3 +1146,161 @@ def head_norm_gate(o, weight, gate, out, n_heads: int, dv: int, eps: float, act:
         dtype_code(gate.dtype), ctypes.c_int(gate.shape[1]), _ptr(out),
         dtype_code(out.dtype), ctypes.c_int(n), ctypes.c_int(n_heads), ctypes.c_int(dv), ctypes.c_float(eps),
         ctypes.c_int(act), _stream()), "head_norm_gate")
+
+
+# --------------------------------------------------------------------------- #
+# attention over a shared low-rank latent
+# --------------------------------------------------------------------------- #
+def latent_prepare(proj, c_weight, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out, kv_cache, n_heads: int,
+                   d: int, rot: int, rank: int, interleaved: bool, eps: float) -> None:
+    """proj [T, ld]: H heads of (d plain + rot rotated) query columns, then the down projection's rank + rot columns.
+    Writes the cache row [c | k_r] of every token (c = the first rank columns divided by their root mean square and
+    multiplied by `c_weight`, k_r = the last rot columns rotated by position) into its page of `kv_cache`
+    [pages, 1, PAGE, rank + rot], and the rotated part of every head's query into the last rot columns of that head
+    in `q_out` [T, H * (rank + rot)]."""
+    _need(proj, "latent prepare proj", None, 2)
+    _need(q_out, "latent prepare q", proj.dtype, 2)
+    _need(kv_cache, "latent prepare cache", proj.dtype, 4)
+    _need(c_weight, "latent prepare norm weight", torch.float32, 1)
+    n = proj.shape[0]
+    if tuple(kv_cache.shape[1:]) != (1, PAGE, rank + rot) or tuple(q_out.shape) != (n, n_heads * (rank + rot)):
+        raise KernelError(f"latent prepare: cache {tuple(kv_cache.shape)} / q {tuple(q_out.shape)} for rank {rank} + {rot}")
+    if c_weight.shape[0] != rank:
+        raise KernelError(f"latent prepare: norm weight of {c_weight.shape[0]}, expected {rank}")
+    if rot:
+        _need(cos, "latent prepare cos", torch.float32, 2)
+        _need(sin, "latent prepare sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError(f"latent prepare: rotary table {tuple(cos.shape)} for {rot} rotated dimensions")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot)):
+        _need(t, f"latent prepare {name}", torch.int32, 1)
+    _need(block_table, "latent prepare block table", torch.int32, 2)
+    _check(lib().mll_latent_prepare(
+        _ptr(proj), _ptr(c_weight), _ptr(cos if rot else None), _ptr(sin if rot else None), _ptr(tok_pos), _ptr(tok_seq),
+        _ptr(seq_slot), _ptr(block_table), _ptr(q_out), _ptr(kv_cache), dtype_code(proj.dtype), ctypes.c_int(n),
+        ctypes.c_int(proj.shape[1]), ctypes.c_int(n_heads), ctypes.c_int(d), ctypes.c_int(rot), ctypes.c_int(rank),
+        ctypes.c_int(int(interleaved)), ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), _stream()),
+        "latent_prepare")
+
+
+# --------------------------------------------------------------------------- #
+# routed feed-forward
+# --------------------------------------------------------------------------- #
+USE_TENSOR_CORE_MOE = True  # tests switch it off to reach the plain products in bfloat16 prompt steps
+
+
+class MoePlan(NamedTuple):
+    """A step's (token, choice) pairs sorted by expert, all on the device (int32): `order` [pairs] place -> pair,
+    `offsets` [E + 1], tiles of up to `rows` places of one expert (`tile_expert`, `tile_row0`, of which the first
+    `n_tiles[0]` count; the lists are sized for the most tiles there can be)."""
+    order: torch.Tensor
+    offsets: torch.Tensor
+    tile_expert: torch.Tensor
+    tile_row0: torch.Tensor
+    n_tiles: torch.Tensor
+    rows: int
+    mma: bool
+
+
+def moe_tile_rows(mma: bool) -> int:
+    return int(lib().mll_moe_mma_rows() if mma else lib().mll_moe_simt_rows())
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int, rows: int) -> int:
+    return n_pairs // rows + n_experts
+
+
+def moe_route(h, w, bias, chosen, weight, top: int) -> None:
+    """chosen [T, top] (int32) = the experts with the largest z = w h + bias (float32; ties: the lower index),
+    weight [T, top] (float32) = softmax over the chosen logits."""
+    _need(h, "moe route h", None, 2)
+    _need(w, "moe route weight", torch.float32, 2)
+    _need(chosen, "moe route chosen", torch.int32, 2)
+    _need(weight, "moe route weights", torch.float32, 2)
+    n, width = h.shape
+    experts = w.shape[0]
+    if w.shape[1] != width or tuple(chosen.shape) != (n, top) or tuple(weight.shape) != (n, top):
+        raise KernelError(f"moe route: h {tuple(h.shape)}, w {tuple(w.shape)}, chosen {tuple(chosen.shape)}")
+    if bias is not None:
+        _need(bias, "moe route bias", torch.float32, 1)
+        if bias.shape[0] != experts:
+            raise KernelError("moe route: one bias per expert is needed")
+    _check(lib().mll_moe_route(_ptr(h), _ptr(w), _ptr(bias), _ptr(chosen), _ptr(weight), dtype_code(h.dtype),
+                               ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(experts), ctypes.c_int(top), _stream()),
+           "moe_route")
+
+
+def moe_sort(chosen, plan: MoePlan, n_experts: int) -> None:
+    n_pairs = chosen.numel()
+    need = moe_max_tiles(n_pairs, n_experts, plan.rows)
+    if (plan.order.numel() < n_pairs or plan.offsets.numel() < n_experts + 1 or plan.tile_expert.numel() < need
+            or plan.tile_row0.numel() < need):
+        raise KernelError("moe sort: the plan's arrays are too short")
+    _check(lib().mll_moe_sort(_ptr(chosen), _ptr(plan.order), _ptr(plan.offsets), _ptr(plan.tile_expert),
+                              _ptr(plan.tile_row0), _ptr(plan.n_tiles), ctypes.c_int(n_pairs), ctypes.c_int(n_experts),
+                              ctypes.c_int(plan.rows), _stream()), "moe_sort")
+
+
+def moe_mma_supported(dtype: torch.dtype, width: int, inter: int) -> bool:
+    return dtype == torch.bfloat16 and hasattr(lib(), "mll_moe_mma_supported") and bool(
+        lib().mll_moe_mma_supported(width, inter))
+
+
+def _plan_args(plan: MoePlan):
+    return (_ptr(plan.order), _ptr(plan.offsets), _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.n_tiles))
+
+
+def moe_gate_up(h, w, act, plan: MoePlan, top: int) -> None:
+    """act[place] = silu(W_gate,e h[token]) * (W_up,e h[token]); w [E, 2 I, D] holds an expert's gate rows, then
+    its up rows; act [pairs, I]."""
+    _need(h, "moe gate_up h", None, 2)
+    _need(w, "moe gate_up w", h.dtype, 3)
+    _need(act, "moe gate_up act", h.dtype, 2)
+    experts, two_inter, width = w.shape
+    inter = two_inter // 2
+    n_pairs = h.shape[0] * top
+    if h.shape[1] != width or tuple(act.shape) != (n_pairs, inter) or two_inter != 2 * inter:
+        raise KernelError(f"moe gate_up: h {tuple(h.shape)}, w {tuple(w.shape)}, act {tuple(act.shape)}")
+    fn = lib().mll_moe_gate_up_mma if plan.mma else lib().mll_moe_gate_up
+    args = (_ptr(h), _ptr(w), _ptr(act), *_plan_args(plan))
+    tiles = ctypes.c_int(moe_max_tiles(n_pairs, experts, plan.rows))
+    if plan.mma:
+        _check(fn(*args, tiles, ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top), _stream()), "moe_gate_up_mma")
+    else:
+        _check(fn(*args, dtype_code(h.dtype), tiles, ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top),
+                  _stream()), "moe_gate_up")
+
+
+def moe_down(act, w, y, pair_weight, plan: MoePlan, top: int) -> None:
+    """y[pair] = weight[pair] * W_down,e act[place] (float32 [pairs, D]); w [E, D, I]."""
+    _need(act, "moe down act", None, 2)
+    _need(w, "moe down w", act.dtype, 3)
+    _need(y, "moe down y", torch.float32, 2)
+    _need(pair_weight, "moe down weights", torch.float32)
+    experts, width, inter = w.shape
+    n_pairs = act.shape[0]
+    if act.shape[1] != inter or tuple(y.shape) != (n_pairs, width) or pair_weight.numel() != n_pairs:
+        raise KernelError(f"moe down: act {tuple(act.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    fn = lib().mll_moe_down_mma if plan.mma else lib().mll_moe_down
+    args = (_ptr(act), _ptr(w), _ptr(y), _ptr(pair_weight), *_plan_args(plan))
+    tiles = ctypes.c_int(moe_max_tiles(n_pairs, experts, plan.rows))
+    if plan.mma:
+        _check(fn(*args, tiles, ctypes.c_int(inter), ctypes.c_int(width), ctypes.c_int(top), _stream()), "moe_down_mma")
+    else:
+        _check(fn(*args, dtype_code(act.dtype), tiles, ctypes.c_int(inter), ctypes.c_int(width), ctypes.c_int(top),
+                  _stream()), "moe_down")
+
+
+def moe_combine(y, other, out, top: int) -> None:
+    """out[t] = y[t * top] + ... + y[t * top + top - 1] (+ other[t]); y float32 [T * top, D]."""
+    _need(y, "moe combine y", torch.float32, 2)
+    _need(out, "moe combine out", None, 2)
+    n, width = out.shape
+    if tuple(y.shape) != (n * top, width):
+        raise KernelError(f"moe combine: y {tuple(y.shape)}, out {tuple(out.shape)}, top {top}")
+    if other is not None:
+        _need(other, "moe combine other", out.dtype, 2)
+        if other.shape != out.shape:
+            raise KernelError("moe combine: the other part's output differs in shape")
+    _check(lib().mll_moe_combine(_ptr(y), _ptr(other), _ptr(out), dtype_code(out.dtype), ctypes.c_int(n),
+                                 ctypes.c_int(width), ctypes.c_int(top), _stream()), "moe_combine")

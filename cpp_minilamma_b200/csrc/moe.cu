@@ -1,0 +1,314 @@
+// A routed feed-forward: every token goes through `top` of E small SwiGLU experts, chosen by a linear router.
+//
+//   z = W_r h + b_r (float32);  the `top` largest z (ties: the lower index);  weights = softmax over those alone
+//   out = sum_j weight_j * W_down,e_j (silu(W_gate,e_j h) * W_up,e_j h)
+//
+// Nothing about the routing ever reaches the host.  The (token, choice) pairs are sorted by expert on the device
+// and cut into tiles of up to MOE_BM rows of one expert; the two products run over that tile list with a grid
+// sized for the most tiles there can be (pairs / MOE_BM + E), blocks past the real count leaving at once.  So a
+// step's launches depend on its number of tokens alone and a decode step can be captured in a graph.
+//
+//   route      a warp per token: E dot products in float32, `top` rounds of a warp-wide arg-max, softmax
+//   sort       one block: counts per expert, their running sums, the tile list, the pairs' places
+//   gate_up    tile x 128 activation columns: act[place, n] = silu(gate) * up, rows gathered by token
+//   down       tile x 128 output columns: y[pair, :] = weight * (W_down act[place]), float32
+//   combine    out[t] = y[t, 0] + ... + y[t, top - 1] (+ another part's output for the same rows), fixed order
+//
+// The products here are the plain form (a thread per output column, the tile's rows in shared memory, float32
+// accumulation in k order); every weight of an expert is read once per tile, which is what a decode step needs.
+// bfloat16 steps with many rows per expert take the tensor-core kernels of moe_mma.cu for the two products.
+#include "common.cuh"
+#include "moe.cuh"
+
+namespace mll {
+
+// ---- route ---------------------------------------------------------------------------------------------------- //
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                                                        const float* __restrict__ bias, int* __restrict__ chosen,
+                                                        float* __restrict__ weight, int n_tokens, int width,
+                                                        int n_experts, int top) {
+  extern __shared__ float z_all[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  float* z = z_all + (size_t)warp * n_experts;
+  const T* row = h + (size_t)t * width;
+  for (int e = 0; e < n_experts; ++e) {
+    const float* we = w + (size_t)e * width;
+    float s = 0.f;
+    for (int i = lane; i < width; i += 32) s = fmaf(to_float(row[i]), we[i], s);
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  float first = 0.f, total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= n_experts) at = j;  // nothing comparable was left (not-a-number logits): any expert that exists
+    if (j == 0) first = best;
+    const float p = expf(best - first);
+    total += p;
+    if (lane == 0) {
+      chosen[(size_t)t * top + j] = at;
+      weight[(size_t)t * top + j] = p;
+      z[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane < top) weight[(size_t)t * top + lane] /= total;
+}
+
+// ---- sort ----------------------------------------------------------------------------------------------------- //
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ chosen, MoePlan plan, int n_pairs,
+                                                        int n_experts, int bm) {
+  extern __shared__ int sort_smem[];
+  int* counts = sort_smem;                 // [E]
+  int* offsets = counts + n_experts;       // [E + 1]
+  int* tile_off = offsets + n_experts + 1; // [E + 1]
+  int* cursor = tile_off + n_experts + 1;  // [E]
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&counts[chosen[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    offsets[0] = 0;
+    tile_off[0] = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offsets[e + 1] = offsets[e] + counts[e];
+      tile_off[e + 1] = tile_off[e] + (counts[e] + bm - 1) / bm;
+    }
+    plan.n_tiles[0] = tile_off[n_experts];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) plan.offsets[e] = offsets[e];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    cursor[e] = offsets[e];
+    for (int i = tile_off[e]; i < tile_off[e + 1]; ++i) {
+      plan.tile_expert[i] = e;
+      plan.tile_row0[i] = offsets[e] + (i - tile_off[e]) * bm;
+    }
+  }
+  __syncthreads();
+  // a pair's place among its expert's rows depends on the order of arrival; no result depends on the place
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) plan.order[atomicAdd(&cursor[chosen[p]], 1)] = p;
+}
+
+// ---- the plain products --------------------------------------------------------------------------------------- //
+constexpr int SIMT_BK = 128;
+
+template <typename T>
+__device__ __forceinline__ void load_chunk(const T* p, int n, bool vec, float* out) {
+  // n <= 16 / sizeof(T) consecutive elements as floats
+  constexpr int PAD = 16 / sizeof(T);
+  if (vec && n == PAD) {
+    if constexpr (sizeof(T) == 4) {
+      const float4 v = *reinterpret_cast<const float4*>(p);
+      out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    } else {
+      const uint4 v = *reinterpret_cast<const uint4*>(p);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+      }
+    }
+  } else {
+    for (int i = 0; i < PAD; ++i) out[i] = i < n ? to_float(p[i]) : 0.f;
+  }
+}
+
+// GATE_UP: A rows are the tokens of the tile's pairs, two accumulators per row (gate, up), out act[place, n].
+// otherwise: A rows are act[place], out y[pair, n] = weight[pair] * sum, float32.
+template <typename T, bool GATE_UP>
+__global__ void __launch_bounds__(128) moe_simt_kernel(MoeProductArgs a) {
+  const int tile = blockIdx.x;
+  if (tile >= a.plan.n_tiles[0]) return;
+  constexpr int PAD = 16 / sizeof(T);
+  __shared__ float a_s[MOE_SIMT_BM][SIMT_BK + 1];
+  __shared__ int row_src[MOE_SIMT_BM];
+  const int e = a.plan.tile_expert[tile], row0 = a.plan.tile_row0[tile];
+  const int rows = min(MOE_SIMT_BM, a.plan.offsets[e + 1] - row0);
+  const int tid = threadIdx.x;
+  const int col = blockIdx.y * 128 + tid;
+  const int K = a.k, N = a.n;
+  if (tid < MOE_SIMT_BM) {
+    int src = -1;
+    if (tid < rows) src = GATE_UP ? a.plan.order[row0 + tid] / a.top : row0 + tid;
+    row_src[tid] = src;
+  }
+  __syncthreads();
+  const T* w0 = (const T*)a.w + ((size_t)e * (GATE_UP ? 2 * N : N) + min(col, N - 1)) * K;
+  const T* w1 = w0 + (size_t)N * K;  // the up row (GATE_UP only)
+  const bool vec = K % PAD == 0 && ((uintptr_t)a.w % 16 == 0);
+  float acc0[MOE_SIMT_BM], acc1[GATE_UP ? MOE_SIMT_BM : 1];
+#pragma unroll
+  for (int r = 0; r < MOE_SIMT_BM; ++r) acc0[r] = 0.f;
+#pragma unroll
+  for (int r = 0; r < (GATE_UP ? MOE_SIMT_BM : 1); ++r) acc1[r] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += SIMT_BK) {
+    const int kn = min(SIMT_BK, K - k0);
+    for (int idx = tid; idx < MOE_SIMT_BM * SIMT_BK; idx += 128) {
+      const int r = idx / SIMT_BK, c = idx % SIMT_BK;
+      const int src = row_src[r];
+      a_s[r][c] = (src >= 0 && c < kn) ? to_float(((const T*)a.a)[(size_t)src * K + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int c = 0; c < kn; c += PAD) {
+      float wv0[PAD], wv1[PAD];
+      load_chunk<T>(w0 + k0 + c, min(PAD, kn - c), vec, wv0);
+      if (GATE_UP) load_chunk<T>(w1 + k0 + c, min(PAD, kn - c), vec, wv1);
+#pragma unroll
+      for (int u = 0; u < PAD; ++u) {
+#pragma unroll
+        for (int r = 0; r < MOE_SIMT_BM; ++r) {
+          const float av = a_s[r][c + u];  // columns past kn hold zeros
+          acc0[r] = fmaf(av, wv0[u], acc0[r]);
+          if (GATE_UP) acc1[r] = fmaf(av, wv1[u], acc1[r]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (col >= N) return;
+#pragma unroll
+  for (int r = 0; r < MOE_SIMT_BM; ++r) {
+    if (r >= rows) break;
+    if (GATE_UP) {
+      const float g = acc0[r];
+      ((T*)a.out)[(size_t)(row0 + r) * N + col] = from_float<T>(g / (1.f + expf(-g)) * acc1[r]);
+    } else {
+      const int pair = a.plan.order[row0 + r];
+      ((float*)a.out)[(size_t)pair * N + col] = a.pair_weight[pair] * acc0[r];
+    }
+  }
+}
+
+// ---- combine -------------------------------------------------------------------------------------------------- //
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ other, T* __restrict__ out,
+                                   size_t total, int width, int top) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width;
+    const int c = (int)(i % width);
+    float s = 0.f;
+    for (int j = 0; j < top; ++j) s += y[(t * top + j) * width + c];
+    if (other) s += to_float(other[i]);
+    out[i] = from_float<T>(s);
+  }
+}
+
+}  // namespace mll
+
+MLL_API int mll_moe_simt_rows() { return MOE_SIMT_BM; }
+
+// h: [n_tokens, width] of `dtype`; w: float32 [n_experts, width]; bias: float32 [n_experts] or null;
+// chosen: int32 [n_tokens, top]; weight: float32 [n_tokens, top].
+MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, int* chosen, float* weight, int dtype,
+                          int n_tokens, int width, int n_experts, int top, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
+              "moe route: bad sizes tokens=%d width=%d experts=%d top=%d", n_tokens, width, n_experts, top);
+  MLL_REQUIRE(n_experts <= 2048, "moe route: %d experts (at most 2048)", n_experts);
+  if (n_tokens == 0) return 0;
+  const size_t smem = (size_t)4 * n_experts * sizeof(float);
+  const int blocks = (n_tokens + 3) / 4;
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::moe_route_kernel<float>), blocks, 128, smem, stream, (const float*)h, w, bias, chosen, weight,
+               n_tokens, width, n_experts, top);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::moe_route_kernel<__nv_bfloat16>), blocks, 128, smem, stream, (const __nv_bfloat16*)h, w, bias,
+               chosen, weight, n_tokens, width, n_experts, top);
+  else
+    MLL_REQUIRE(false, "moe route: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// chosen: int32 [n_pairs]; order: int32 [n_pairs]; offsets: int32 [n_experts + 1]; tile_expert, tile_row0: int32
+// [n_pairs / bm + n_experts]; n_tiles: int32 [1].
+MLL_API int mll_moe_sort(const int* chosen, int* order, int* offsets, int* tile_expert, int* tile_row0, int* n_tiles,
+                         int n_pairs, int n_experts, int bm, cudaStream_t stream) {
+  MLL_REQUIRE(n_pairs >= 0 && n_experts > 0 && n_experts <= 2048 && bm > 0, "moe sort: bad sizes");
+  if (n_pairs == 0) return 0;
+  const size_t smem = (size_t)(4 * n_experts + 2) * sizeof(int);
+  MLL_LAUNCH((mll::moe_sort_kernel), 1, 1024, smem, stream, chosen,
+             mll::MoePlan{order, offsets, tile_expert, tile_row0, n_tiles}, n_pairs, n_experts, bm);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+static int moe_check(const char* what, int max_tiles, int k, int n, int top) {
+  MLL_REQUIRE(max_tiles > 0 && k > 0 && n > 0 && top > 0, "%s: bad sizes tiles=%d k=%d n=%d top=%d", what, max_tiles, k, n, top);
+  MLL_REQUIRE((n + 127) / 128 <= 65535, "%s: %d columns are too many for one launch", what, n);
+  return 0;
+}
+
+// act[place, :] = silu(W_gate,e h[token]) * (W_up,e h[token]) for every place of the sorted pairs.
+// h: [n_tokens, width]; w: [n_experts, 2 inter, width] (an expert's gate rows, then its up rows); act: [n_pairs, inter].
+MLL_API int mll_moe_gate_up(const void* h, const void* w, void* act, const int* order, const int* offsets,
+                            const int* tile_expert, const int* tile_row0, const int* n_tiles, int dtype, int max_tiles,
+                            int width, int inter, int top, cudaStream_t stream) {
+  if (moe_check("moe gate_up", max_tiles, width, inter, top)) return -1;
+  mll::MoeProductArgs a{h, w, act, nullptr, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert, (int*)tile_row0,
+                                                         (int*)n_tiles}, width, inter, top};
+  const dim3 grid(max_tiles, (inter + 127) / 128);
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::moe_simt_kernel<float, true>), grid, 128, 0, stream, a);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, true>), grid, 128, 0, stream, a);
+  else
+    MLL_REQUIRE(false, "moe gate_up: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// y[pair, :] = weight[pair] * W_down,e act[place] (float32).  act: [n_pairs, inter]; w: [n_experts, width, inter].
+MLL_API int mll_moe_down(const void* act, const void* w, float* y, const float* pair_weight, const int* order,
+                         const int* offsets, const int* tile_expert, const int* tile_row0, const int* n_tiles, int dtype,
+                         int max_tiles, int inter, int width, int top, cudaStream_t stream) {
+  if (moe_check("moe down", max_tiles, inter, width, top)) return -1;
+  mll::MoeProductArgs a{act, w, y, pair_weight, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert,
+                                                             (int*)tile_row0, (int*)n_tiles}, inter, width, top};
+  const dim3 grid(max_tiles, (width + 127) / 128);
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::moe_simt_kernel<float, false>), grid, 128, 0, stream, a);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, false>), grid, 128, 0, stream, a);
+  else
+    MLL_REQUIRE(false, "moe down: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// out[t, :] = y[t * top, :] + ... + y[t * top + top - 1, :] (+ other[t, :]); y float32, other and out of `dtype`.
+MLL_API int mll_moe_combine(const float* y, const void* other, void* out, int dtype, int n_tokens, int width, int top,
+                            cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && width > 0 && top > 0, "moe combine: bad sizes");
+  if (n_tokens == 0) return 0;
+  const size_t total = (size_t)n_tokens * width;
+  long long blocks = (long long)((total + 255) / 256);
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::moe_combine_kernel<float>), (int)blocks, 256, 0, stream, y, (const float*)other, (float*)out, total,
+               width, top);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::moe_combine_kernel<__nv_bfloat16>), (int)blocks, 256, 0, stream, y, (const __nv_bfloat16*)other,
+               (__nv_bfloat16*)out, total, width, top);
+  else
+    MLL_REQUIRE(false, "moe combine: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}

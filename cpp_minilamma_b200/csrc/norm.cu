@@ -164,6 +164,61 @@ int launch_add_rmsnorm(float* x, const void* delta, const void* delta2, const fl
   return 0;
 }
 
+// Layer norm with weight and bias, fused with the residual add like the kernel above:
+//   x[t, :] += delta[t, :];   out[t, i] = (x[t, i] - mean) / sqrt(var + eps) * w[i] + b[i]
+// with var the mean of the squared deviations from the mean (two passes over the row, which stays in shared
+// memory; float32 throughout).  One block per output row; `rows` gathers as above.
+template <typename DeltaT, typename OutT>
+__global__ void add_layernorm_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
+                                     const float* __restrict__ weight, const float* __restrict__ bias,
+                                     OutT* __restrict__ out, const int* __restrict__ rows, int width, float eps) {
+  extern __shared__ float row_buf[];
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * width;
+  const DeltaT* dr = delta ? delta + (size_t)src * width : nullptr;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) {
+      v += to_float(dr[i]);
+      if (!rows) xr[i] = v;
+    }
+    row_buf[i] = v;
+    sum += v;
+  }
+  const float mean = block_sum(sum, scratch) / (float)width;
+  float dev = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float c = row_buf[i] - mean;
+    dev += c * c;
+  }
+  const float scale = 1.f / sqrtf(block_sum(dev, scratch) / (float)width + eps);
+  OutT* o = out + (size_t)r * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    o[i] = from_float<OutT>((row_buf[i] - mean) * scale * weight[i] + (bias ? bias[i] : 0.f));
+}
+
+template <typename DeltaT, typename OutT>
+int launch_add_layernorm(float* x, const void* delta, const float* weight, const float* bias, void* out,
+                         const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  const size_t smem = (size_t)width * sizeof(float);
+  auto kernel = add_layernorm_kernel<DeltaT, OutT>;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+      mll_set_error("layernorm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+      return (int)err;
+    }
+  }
+  MLL_LAUNCH((kernel), n_rows, threads, smem, stream, x, (const DeltaT*)delta, weight, bias, (OutT*)out, rows, width,
+             eps);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
 // Finishes a norm whose rows were left without their factor (RowNormIn), for a product that cannot do
 // it itself: out[m, i] = values[m, i] * factor(m).  One block per row.
 __global__ void apply_row_norm_kernel(const __nv_bfloat16* __restrict__ values, RowNormIn in,
@@ -224,4 +279,24 @@ MLL_API int mll_add_rmsnorm(float* x, const void* delta, const float* weight, vo
                             const int* rows, int act_dtype, int n_rows, int width, float eps,
                             cudaStream_t stream) {
   return mll_add2_rmsnorm(x, delta, nullptr, weight, out, rows, act_dtype, act_dtype, n_rows, width, eps, stream);
+}
+
+// Layer norm with weight and (optional) bias after the residual add; arguments as for mll_add2_rmsnorm.
+MLL_API int mll_add_layernorm(float* x, const void* delta, const float* weight, const float* bias, void* out,
+                              const int* rows, int delta_dtype, int out_dtype, int n_rows, int width, float eps,
+                              cudaStream_t stream) {
+  MLL_REQUIRE(n_rows >= 0 && width > 0, "layernorm: bad sizes rows=%d width=%d", n_rows, width);
+  MLL_REQUIRE(width <= 50 * 1024, "layernorm: width %d exceeds the 51200 floats one block can hold", width);
+  MLL_REQUIRE(eps >= 0.f, "layernorm: eps must be non-negative");
+  if (n_rows == 0) return 0;
+  if (delta_dtype == MLL_F32 && out_dtype == MLL_F32)
+    return mll::launch_add_layernorm<float, float>(x, delta, weight, bias, out, rows, n_rows, width, eps, stream);
+  if (delta_dtype == MLL_BF16 && out_dtype == MLL_BF16)
+    return mll::launch_add_layernorm<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, bias, out, rows, n_rows, width,
+                                                                   eps, stream);
+  if (delta_dtype == MLL_BF16 && out_dtype == MLL_F32)
+    return mll::launch_add_layernorm<__nv_bfloat16, float>(x, delta, weight, bias, out, rows, n_rows, width, eps,
+                                                           stream);
+  MLL_REQUIRE(false, "layernorm: dtypes %d / %d", delta_dtype, out_dtype);
+  return -1;
 }

@@ -48,6 +48,7 @@ class Model:
                 mixer=build_part("mixer", layer_spec.mixer, self.ctx),
                 feed_forward=build_part("feed_forward", layer_spec.feed_forward, self.ctx),
                 norms={name: build_part("norm", s, self.ctx) for name, s in layer_spec.norms.items()}))
+        self.stream_ops = [build_part("stream_op", s, self.ctx) for s in spec.stream_ops]
         self.final_norm = build_part("norm", spec.final_norm, self.ctx)
         self.lm_head = build_part("lm_head", spec.lm_head, self.ctx)
         for i, entry in enumerate(spec.schedule):
@@ -55,6 +56,9 @@ class Model:
                 raise ValueError(f"schedule entry {i} names layer {entry.layer}, the model has {len(self.layers)}")
             if entry.cache_of is not None and not 0 <= entry.cache_of < i:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {entry.cache_of}, which is not earlier")
+            if entry.enter is not None and not 0 <= entry.enter[0] < len(self.stream_ops):
+                raise ValueError(f"schedule entry {i} names stream operation {entry.enter[0]}, the model has "
+                                 f"{len(self.stream_ops)}")
         self.bound = False
 
     # ---- weights ------------------------------------------------------------ #
@@ -62,6 +66,7 @@ class Model:
         parts = [self.embedding]
         for layer in self.layers:
             parts.extend(layer.parts())
+        parts.extend(self.stream_ops)
         parts.extend([self.final_norm, self.lm_head])
         return parts
 
@@ -98,6 +103,8 @@ class Model:
         total = self.final_norm.parameter_bytes() + self.lm_head.parameter_bytes()
         for entry in self.spec.schedule:
             total += sum(p.parameter_bytes() for p in self.layers[entry.layer].parts())
+            if entry.enter is not None:
+                total += self.stream_ops[entry.enter[0]].parameter_bytes()
         return total
 
     def capturable(self) -> bool:
@@ -118,13 +125,22 @@ class Model:
         x = self.embedding.forward(step, tokens)
         pending = None
         schedule = self.spec.schedule
+        x0 = None
+        if self.stream_ops:  # they read the stream as the embedding left it
+            x0 = step.ws.buffer("x0", tuple(x.shape), torch.float32)
+            x0.copy_(x)
         for i, entry in enumerate(schedule):
             layer = self.layers[entry.layer]
+            if entry.enter is not None:
+                self.stream_ops[entry.enter[0]].forward(step, x, pending, x0, entry.enter[1])
+                pending = None
             if layer.block.first_reader(layer) is None:
                 pending = layer.block.forward(step, x, pending, layer, cache.view(i))
                 continue
             # this arrangement can fold a norm into the products around it: tell it who reads the stream next
-            follower = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            # (not across an operation on the stream: the rows the next layer reads are not this layer's)
+            follower = (self.layers[schedule[i + 1].layer]
+                        if i + 1 < len(schedule) and schedule[i + 1].enter is None else None)
             reader = follower.block.first_reader(follower) if follower else None
             pending = layer.block.forward(step, x, pending, layer, cache.view(i), next_reader=reader)
         if want_rows is None or want_rows.shape[0] == 0:

@@ -42,12 +42,14 @@ class WeightSpec:
     weights cannot be drawn for such a tensor.
     init: how the random-weights mode fills it: "normal" N(0, matrix_std), "norm"
     1 + N(0, norm_std), "zeros", "ones".
+    optional: a folder may leave the tensor out; it then stands as ones ("norm", "ones") or zeros.
     """
 
     name: str
     shape: Tuple[int, ...]
     kind: str = "matrix"
     init: str = "normal"
+    optional: bool = False
 
 
 @dataclass
@@ -67,10 +69,12 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.  `cache_of` names an earlier entry (by its index in the
-    schedule) whose cache this entry reads instead of owning one."""
+    schedule) whose cache this entry reads instead of owning one.  `enter` = (index into the model's
+    `stream_ops`, pass number): that operation rewrites the residual stream right before the layer runs."""
 
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[Tuple[int, int]] = None
 
 
 @dataclass
@@ -84,6 +88,7 @@ class ModelSpec:
     final_norm: PartSpec
     lm_head: PartSpec
     stop_token_ids: List[int] = field(default_factory=list)
+    stream_ops: List[PartSpec] = field(default_factory=list)  # operations on the stream between layers (ScheduleEntry.enter)
 
 
 # --------------------------------------------------------------------------- #
@@ -93,12 +98,15 @@ class ModelSpec:
 class KVNeed:
     """Keys and values per position: pages of [n_kv_heads, PAGE, head_dim].  `window` > 0
     means only the last `window` positions are ever read.  `v_head_dim` > 0: the values' head size
-    where it differs from the keys' (value pages are then [n_kv_heads, PAGE, v_head_dim])."""
+    where it differs from the keys' (value pages are then [n_kv_heads, PAGE, v_head_dim]).  `v_in_k`: the values
+    are the leading `v_head_dim` columns of the key rows, so no value pages exist (a layer that caches one latent
+    row per position and reads it as key and as value)."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    v_in_k: bool = False
 
 
 @dataclass(frozen=True)
@@ -285,6 +293,17 @@ class Norm(Part):
         return None
 
 
+class StreamOp(Part):
+    """An operation on the residual stream between two layers (a schedule entry's `enter`)."""
+
+    role = "stream_op"
+
+    def forward(self, step, x: torch.Tensor, pending, x0: torch.Tensor, pass_number: int) -> None:
+        """Rewrite the float32 stream `x` [T, D] in place.  `pending` is the output of the part before, still
+        to be added to x first (a tensor or None); `x0` is the stream as the embedding left it."""
+        raise NotImplementedError
+
+
 class Mixer(Part):
     role = "mixer"
     takes_prenormed = False  # True: `h` may be a PreNormed
@@ -332,7 +351,7 @@ class Block(Part):
 # --------------------------------------------------------------------------- #
 _PARTS: Dict[str, Dict[str, Callable]] = {
     "position_encoding": {}, "norm": {}, "mixer": {}, "feed_forward": {}, "block": {},
-    "embedding": {}, "lm_head": {},
+    "embedding": {}, "lm_head": {}, "stream_op": {},
 }
 
 

@@ -7,6 +7,11 @@
                                       and j > i - window where window > 0
     out = W_o concat_heads(softmax(score) v)
 
+Options beyond that, each a parameter: a query temperature (q at position p times 1 + coef * ln(floor((p + 1) /
+every) + 1)); a sink in the softmax (weights exp(s_j) / (1 + sum_j exp(s_j)): one more key that scores 0 and carries
+no value); an output gate read from the mixer's own input, one number per head (head h's output times
+sigmoid(W_g h)_h) or one per element, applied before W_o.
+
 Chunks count from position 0 of the sequence, not from where a step's tokens begin.  Keys and values live in
 the paged cache; a chunked layer asks the cache to keep only what its chunk can still reach (a window of one
 chunk), so pages of finished chunks go back to the pool.  Every constant is a parameter; the Llama attention
@@ -34,7 +39,10 @@ class ChunkedAttention(Mixer):
       position                                      PartSpec of a rotary encoding over `rotary_dims` dimensions, or None
       rotary_dims                                   how many leading dimensions of a head are rotated
       qk_norm                                       None or {"q": tensor name, "k": tensor name, "eps": float}
-      names                                         {"q","k","v","o"}: tensor names
+      q_temp                                        None or {"coef": float, "every": int}: the query temperature
+      sink                                          True: the softmax's denominator has one more term exp(0)
+      gate                                          None, "head" or "element": an output gate sigmoid(W_g h), names["g"]
+      names                                         {"q","k","v","o"} (and "g"): tensor names
     """
 
     capturable = True
@@ -50,6 +58,14 @@ class ChunkedAttention(Mixer):
         self.window = int(params.get("window") or 0)
         self.names = dict(params["names"])
         self.qk_norm = dict(params["qk_norm"]) if params.get("qk_norm") else None
+        q_temp = params.get("q_temp")
+        self.q_temp = (float(q_temp["coef"]), int(q_temp["every"])) if q_temp else None
+        self.sink = bool(params.get("sink", False))
+        self.gate = params.get("gate") or None
+        if self.gate not in (None, "head", "element"):
+            raise ValueError(f"attention: gate {self.gate!r} is neither 'head' nor 'element'")
+        if self.q_temp and self.q_temp[1] < 1:
+            raise ValueError(f"attention: a query temperature every {self.q_temp[1]} positions")
         self.rot = int(params.get("rotary_dims") or 0) if params.get("position") else 0
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
@@ -68,16 +84,22 @@ class ChunkedAttention(Mixer):
                  WeightSpec(self.names["k"], (self.n_kv_heads * self.d, D)),
                  WeightSpec(self.names["v"], (self.n_kv_heads * self.dv, D)),
                  WeightSpec(self.names["o"], (D, self.n_heads * self.dv))]
+        if self.gate:
+            specs.append(WeightSpec(self.names["g"], (self._gate_width(), D)))
         if self.qk_norm:
             specs.append(WeightSpec(self.qk_norm["q"], (self.n_heads * self.d,), kind="vector", init="norm"))
             specs.append(WeightSpec(self.qk_norm["k"], (self.n_kv_heads * self.d,), kind="vector", init="norm"))
         return specs
 
+    def _gate_width(self) -> int:
+        return self.n_heads if self.gate == "head" else self.n_heads * self.dv
+
     def bind(self, store) -> None:
-        mats = [store.take(self.names[p]) for p in ("q", "k", "v")]
+        # the gate reads the same rows as q, k and v: its matrix rides behind theirs in the one fused product
+        mats = [store.take(self.names[p]) for p in (("q", "k", "v", "g") if self.gate else ("q", "k", "v"))]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
-        self.qkv = Linear(torch.cat(mats, dim=0), self.names["q"] + "+k+v")
+        self.qkv = Linear(torch.cat(mats, dim=0), self.names["q"] + "+k+v" + ("+g" if self.gate else ""))
         del mats
         self.o = Linear(store.take(self.names["o"]), self.names["o"])
         if self.qk_norm:
@@ -130,33 +152,42 @@ class ChunkedAttention(Mixer):
                                   step.seq_slot, cache.block_table, q, cache.k, cache.v, self.n_heads,
                                   self.n_kv_heads, self.d, self.dv, self.rot,
                                   bool(self.position.interleaved) if self.position is not None else False,
-                                  float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
+                                  float(self.qk_norm["eps"]) if self.qk_norm else 0.0, q_temp=self.q_temp)
         out = step.ws.buffer("attn", (T, self.n_heads * self.dv), act)
-        if (step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+        self._attend(step, q, cache, out)
+        if self.gate:
+            K.heads_gate(out, qkv, self.n_heads * self.d + self.n_kv_heads * (self.d + self.dv), out, self.n_heads,
+                         self.dv, per_head=self.gate == "head")
+        return self.o.forward(step, out, "o")
+
+    def _attend(self, step, q, cache, out) -> None:
+        act = self.ctx.act_dtype
+        if (not self.sink and step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
                 and not (self.chunk and self.window) and act == torch.bfloat16):
             # single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed or
             # mma.sync), which take the chunk as the key range's start; one block per (sequence, kv head)
             K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, None, out,
                                step.n_seqs, self.n_heads, self.n_kv_heads, self.d, 1, self.window, self.scale,
                                chunk=self.chunk)
-            return self.o.forward(step, out, "o")
+            return
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
-        if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
+        if tiles and not self.sink and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
             # keys and values of one head size that the Llama attention's tcgen05 prompt kernel takes: that kernel,
             # which knows the chunk mask too
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                 tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out,
                                 tiles["tile_seq"].shape[0], self.n_heads, self.n_kv_heads, self.d, self.window,
                                 self.scale, wide_tiles=(tiles["wide_seq"], tiles["wide_row0"]), chunk=self.chunk)
-            return self.o.forward(step, out, "o")
+            return
         if tiles and self._tensor_cores():
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out, self.n_heads,
-                                    self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale)
-            return self.o.forward(step, out, "o")
+                                    self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale,
+                                    sink=self.sink)
+            return
         K.local_attention(q, cache.k, cache.v, step.tok_pos, step.tok_seq, step.seq_slot, cache.block_table, out,
-                          self.n_heads, self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale)
-        return self.o.forward(step, out, "o")
+                          self.n_heads, self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale,
+                          sink=self.sink)
 
 
 register_part("mixer", "chunked_attention", ChunkedAttention)

@@ -34,12 +34,13 @@ class Linear:
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, step, x, out_name: str, out_dtype: Optional[torch.dtype] = None,
-                into: Optional[ResidualTarget] = None):
+                into: Optional[ResidualTarget] = None, out: Optional[torch.Tensor] = None):
         """x [T, K] in the activation dtype -> [T, N] in `out_dtype` (default: x's dtype).
 
         x may be a `PreNormed` (bfloat16 only: nothing else makes one).  With `into`, the product may add
         its result to the residual stream and return a `PreNormed` for the norm named there; it does so for
-        the few rows of a decode step, and returns the plain result otherwise."""
+        the few rows of a decode step, and returns the plain result otherwise.  `out`: the tensor to write to
+        ([T, N] of `out_dtype`, contiguous) instead of the workspace buffer `out_name`."""
         row_norm = None
         if isinstance(x, PreNormed):
             row_norm = K.RowNorm(x.sumsq, x.partials, x.eps)
@@ -50,6 +51,9 @@ class Linear:
         out_dtype = out_dtype or x.dtype
         w = self.weight
         ws = step.ws
+        if out is not None and (into is not None or out.dtype != out_dtype or tuple(out.shape) != (rows, self.out_features)):
+            raise ValueError(f"{self.name}: the given output {tuple(out.shape)} {out.dtype} does not fit the product")
+        given = out
         if w.dtype == torch.float32:
             if torch.backends.cuda.matmul.allow_tf32:
                 raise RuntimeError(f"{self.name}: TF32 is enabled; the float32 path needs true 32-bit products")
@@ -64,12 +68,12 @@ class Linear:
                 K.cast(x, wide)
                 x = wide
             if out_dtype == torch.float32:
-                out = ws.buffer(out_name, (rows, self.out_features), torch.float32)
+                out = given if given is not None else ws.buffer(out_name, (rows, self.out_features), torch.float32)
                 torch.mm(x, w.t(), out=out)
                 return out
             wide_out = ws.buffer(out_name + ".y32", (rows, self.out_features), torch.float32)
             torch.mm(x, w.t(), out=wide_out)
-            out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
+            out = given if given is not None else ws.buffer(out_name, (rows, self.out_features), out_dtype)
             K.cast(wide_out, out)
             return out
         # bfloat16 weight
@@ -80,7 +84,7 @@ class Linear:
             made = self._into_residual(ws, x, row_norm, out_name, into)
             if made is not None:
                 return made
-        out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
+        out = given if given is not None else ws.buffer(out_name, (rows, self.out_features), out_dtype)
         if rows <= step.small_rows and K.small_linear(x, w, None, out,
                                                        K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16,
                                                        row_norm):

@@ -1,0 +1,116 @@
+"""A routed feed-forward: every token goes through `top` of E small SwiGLU experts, plus a shared one.
+
+    z       = W_r h + b_r                          float32 router logits
+    chosen  = the `top` experts with the largest z (ties: the lower index)
+    weights = softmax over the chosen logits alone
+    out     = sum_j weights_j * expert_{chosen_j}(h)  +  shared(h)        expert(h) = W_down (silu(W_gate h) * W_up h)
+
+The experts' matrices are stacked ([E, 2 I, D] gate rows then up rows, and [E, D, I]); the routing stays on the
+device: the (token, choice) pairs are sorted by expert there and the two products run over tiles of one expert's
+rows (csrc/moe.cu), so a step's launches follow from its number of tokens alone and decode steps replay from a
+graph.  bfloat16 steps with enough rows per expert take the tensor-core kernels.  The shared expert is a dense
+SwiGLU feed-forward of its own width (the `swiglu` part); its output is added in the same pass that sums a token's
+experts.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import BuildContext, FeedForward, PartSpec, WeightSpec, build_part, register_part
+
+
+class RoutedFeedForward(FeedForward):
+    """params:
+      experts, top, intermediate      number of experts, experts per token, an expert's width
+      router_bias                     True: the router has a bias
+      names                           {"router", "router_bias", "expert": a pattern with {e} and {p}} where p is one of
+                                      gate, up, down
+      shared                          None, or the params of a `swiglu` part that every token also goes through
+    """
+
+    capturable = True
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.inter = int(params["intermediate"])
+        self.names = dict(params["names"])
+        self.has_bias = bool(params.get("router_bias", False))
+        if not 1 <= self.top <= min(self.experts, 32):
+            raise ValueError(f"routed feed-forward: top {self.top} of {self.experts} experts (at most 32)")
+        self.shared = build_part("feed_forward", PartSpec("swiglu", dict(params["shared"])), ctx) \
+            if params.get("shared") else None
+        self.router: Optional[torch.Tensor] = None
+        self.router_bias: Optional[torch.Tensor] = None
+        self.gate_up: Optional[torch.Tensor] = None
+        self.down: Optional[torch.Tensor] = None
+
+    def _expert(self, e: int, p: str) -> str:
+        return self.names["expert"].format(e=e, p=p)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D = self.ctx.hidden_size
+        specs = [WeightSpec(self.names["router"], (self.experts, D), kind="vector", init="normal")]
+        if self.has_bias:
+            specs.append(WeightSpec(self.names["router_bias"], (self.experts,), kind="vector", init="normal"))
+        for e in range(self.experts):
+            specs += [WeightSpec(self._expert(e, "gate"), (self.inter, D)), WeightSpec(self._expert(e, "up"), (self.inter, D)),
+                      WeightSpec(self._expert(e, "down"), (D, self.inter))]
+        return specs + (self.shared.weight_specs() if self.shared is not None else [])
+
+    def bind(self, store) -> None:
+        self.router = store.take(self.names["router"])  # float32: the logits are 32-bit whatever the run's dtype
+        self.router_bias = store.take(self.names["router_bias"]) if self.has_bias else None
+        act = self.ctx.act_dtype
+        gate_up, down = [], []
+        for e in range(self.experts):
+            gate_up.append(torch.cat([store.take(self._expert(e, "gate")).to(act), store.take(self._expert(e, "up")).to(act)]))
+            down.append(store.take(self._expert(e, "down")).to(act))
+        self.gate_up = torch.stack(gate_up).contiguous()
+        self.down = torch.stack(down).contiguous()
+        if self.shared is not None:
+            self.shared.bind(store)
+
+    def parameter_bytes(self) -> int:
+        """What a step reads at most: the router, `top` experts a token (a large batch touches them all) and the
+        shared expert."""
+        size = self.gate_up.element_size()
+        per_expert = (self.gate_up.shape[1] * self.gate_up.shape[2] + self.down.shape[1] * self.down.shape[2]) * size
+        return (self.router.numel() * 4 + self.experts * per_expert
+                + (self.shared.parameter_bytes() if self.shared is not None else 0))
+
+    def _plan(self, step, n_pairs: int, mma: bool) -> K.MoePlan:
+        rows = K.moe_tile_rows(mma)
+        tiles = K.moe_max_tiles(n_pairs, self.experts, rows)
+        ws = step.ws
+        return K.MoePlan(ws.buffer("moe.order", (n_pairs,), torch.int32), ws.buffer("moe.offsets", (self.experts + 1,), torch.int32),
+                         ws.buffer("moe.tile_expert", (tiles,), torch.int32), ws.buffer("moe.tile_row0", (tiles,), torch.int32),
+                         ws.buffer("moe.n_tiles", (1,), torch.int32), rows, mma)
+
+    def forward(self, step, h, into=None):
+        T, D = h.shape
+        ws = step.ws
+        act = self.ctx.act_dtype
+        n_pairs = T * self.top
+        chosen = ws.buffer("moe.chosen", (T, self.top), torch.int32)
+        weight = ws.buffer("moe.weight", (T, self.top), torch.float32)
+        K.moe_route(h, self.router, self.router_bias, chosen, weight, self.top)
+        # tensor cores pay once an expert's tiles fill: with few rows per expert every weight is read for a handful of rows
+        mma = (n_pairs >= 8 * self.experts and K.USE_TENSOR_CORE_MOE and K.moe_mma_supported(act, D, self.inter))
+        plan = self._plan(step, n_pairs, mma)
+        K.moe_sort(chosen, plan, self.experts)
+        hidden = ws.buffer("moe.act", (n_pairs, self.inter), act)
+        K.moe_gate_up(h, self.gate_up, hidden, plan, self.top)
+        y = ws.buffer("moe.y", (n_pairs, D), torch.float32)
+        K.moe_down(hidden, self.down, y, weight, plan, self.top)
+        shared = self.shared.forward(step, h) if self.shared is not None else None
+        out = ws.buffer("moe.out", (T, D), act)
+        K.moe_combine(y, shared, out, self.top)
+        return out
+
+
+register_part("feed_forward", "routed", RoutedFeedForward)

@@ -46,7 +46,7 @@ _INTS = (torch.int32, torch.int64)
 def check_tensors(found: Dict[str, tuple], specs: Sequence[WeightSpec]) -> None:
     """found: name -> (dtype, shape).  Raises one WeightError for all faults."""
     wanted = {s.name: s for s in specs}
-    missing = [n for n in wanted if n not in found]
+    missing = [n for n, s in wanted.items() if n not in found and not s.optional]
     unexpected = sorted(n for n in found if n not in wanted)
     wrong = []
     for name, spec in wanted.items():
@@ -77,6 +77,10 @@ def load_tensors(folder, specs: Sequence[WeightSpec], run_dtype: torch.dtype, de
         check_tensors({n: (e.dtype, e.shape) for n, e in files.entries.items()}, specs)
         out: Dict[str, torch.Tensor] = {}
         for spec in specs:
+            if spec.optional and spec.name not in files.entries:
+                fill = torch.ones if spec.init in ("norm", "ones") else torch.zeros
+                out[spec.name] = fill(tuple(spec.shape), dtype=placement_dtype(spec, run_dtype, run_dtype), device=device)
+                continue
             host = files.read(spec.name)
             out[spec.name] = host.to(device=device, dtype=placement_dtype(spec, host.dtype, run_dtype)).contiguous()
         return out
