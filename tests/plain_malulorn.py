@@ -167,6 +167,12 @@ def route(h, W, pre, top):
     return chosen, e / e.sum(axis=1, keepdims=True)
 
 
+def route_margin(h, W, pre, top):
+    """[T]: how far the last chosen logit lies above the first one left out (infinite when every expert is chosen)."""
+    z = np.sort(h @ W[pre + "router"].T + W[pre + "router.b"], axis=1)[:, ::-1]
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else np.full(h.shape[0], np.inf)
+
+
 def mixture_of_experts(h, W, pre, mlp):
     chosen, weights = route(h, W, pre, mlp["router"]["top"])
     out = np.zeros_like(h)
@@ -193,8 +199,9 @@ def schedule(config):
     return order + [(i, None, False) for i in range(loop["stop"], n)]
 
 
-def forward(config, W, tokens, with_layers=False):
-    """logits [T, vocab] of a whole sequence; with_layers: also the stream after every layer run."""
+def forward(config, W, tokens, with_layers=False, margins=None):
+    """logits [T, vocab] of a whole sequence; with_layers: also the stream after every layer run; margins: a list
+    that receives, per routed layer run, every token's `route_margin`."""
     eps = config["norm"]["eps"]
     x = W["embed"][np.asarray(tokens)]
     x0 = x.copy()
@@ -213,7 +220,12 @@ def forward(config, W, tokens, with_layers=False):
             raise ValueError(f"layer type {layer['type']}")
         if layer.get("mlp"):
             h = layer_norm(x, W[pre + "norm2"], W[pre + "norm2.b"], eps)
-            x = x + mixture_of_experts(h, W, pre + "mlp.", layer["mlp"])
+            if layer["mlp"]["kind"] == "dense":
+                x = x + expert(h, W, pre + "mlp.")
+            else:
+                if margins is not None:
+                    margins.append(route_margin(h, W, pre + "mlp.", layer["mlp"]["router"]["top"]))
+                x = x + mixture_of_experts(h, W, pre + "mlp.", layer["mlp"])
         after.append(x.copy())
     logits = layer_norm(x, W["final.norm"], W["final.norm.b"], eps) @ W["head"].T
     return (logits, np.stack(after)) if with_layers else logits
