@@ -429,6 +429,64 @@ def kupirax_config(size):
                                 "norm": {"eps": 1e-6}, "layers": group * s["groups"], "torch_dtype": "bfloat16"})
 
 
+def malulorn_config(size):
+    """Three layers (attention with a sink, latent attention, attention with a sink) that run twice in a row, so
+    six layer runs like the Llama decoder beside it; every token goes through 2 of 16 experts and a shared one, whose
+    widths add up to the Llama decoder's feed-forward (equal work per token; the experts' total is 4.5 times that)."""
+    import cpp_minilamma_b200 as ml
+    s = DESIGN_SIZES[size]
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": s["ff"] // 4}, "shared": {"ff": s["ff"] // 2}}
+    sink = {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                      "q_temp": {"coef": 0.1, "every": 1024}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": s["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 192 ** -0.5,
+                        "rot": {"base": 500000.0, "dims": 64}}}
+    return ml.config_from_dict({"architecture": "Malulorn", "vocab": s["vocab"], "width": s["width"],
+                                "norm": {"eps": 1e-5}, "layers": [sink, latent, sink],
+                                "loop": {"start": 0, "stop": 3, "times": s["groups"]}, "torch_dtype": "bfloat16"})
+
+
+def malulorn_rooflines(size, tokens, batch, context, peaks):
+    """As `design_rooflines`, for the kernels of the Malulorn decoder and their like in the Llama decoder."""
+    s = DESIGN_SIZES[size]
+    H, G, d, D, ff = s["heads"], s["kv_heads"], 128, s["width"], s["ff"]
+    rank, row = 192, 256
+    E, top, eff = 16, 2, ff // 4
+    causal = tokens * (tokens + 1) // 2
+    out = {}
+    # prompt attention: the sink layers (d = dv = 128) and the latent layers (keys of 256, values of 192, one kv head)
+    out["malulorn", "prefill", "attention_prefill"] = ("tensor", 2.0 * H * causal * 2 * d)
+    out["malulorn", "prefill", "local_attention_mma"] = ("tensor", 2.0 * H * causal * (d + d + row + rank) / 2)  # mean of the two kinds
+    out["llama", "prefill", "attention_prefill"] = ("tensor", 2.0 * H * causal * 2 * d)
+    qkv = (H * d + 2 * G * d) * 2
+    out["malulorn", "prefill", "local_attention_prepare"] = ("hbm", tokens * 2 * qkv)
+    out["malulorn", "prefill", "latent_prepare"] = ("hbm", tokens * (H * 64 * 4 + row * 4 + rank * 2))
+    out["llama", "prefill", "rope_cache_write"] = ("hbm", tokens * 2 * qkv)
+    out["malulorn", "decode", "local_attention_prepare"] = ("hbm", batch * 2 * qkv)
+    # single tokens: keys and values once (the latent layers read one row of 256 per position)
+    sink_bytes, latent_bytes = batch * context * G * 2 * d * 2, batch * context * row * 2
+    out["malulorn", "decode", "attention_decode"] = ("hbm", sink_bytes)
+    out["malulorn", "decode", "local_attention_heads"] = ("hbm", (2 * sink_bytes + latent_bytes) / 3)  # if all three layers run here
+    out["malulorn", "decode", "local_attention"] = ("hbm", (2 * sink_bytes + latent_bytes) / 3)
+    out["llama", "decode", "attention_decode"] = ("hbm", sink_bytes)
+    # the experts' products: FLOPs of the chosen experts in prompts; in decode steps every expert's weights once
+    out["malulorn", "prefill", "moe_gate_up_mma"] = ("tensor", 2.0 * tokens * top * 2 * eff * D)
+    out["malulorn", "prefill", "moe_down_mma"] = ("tensor", 2.0 * tokens * top * eff * D)
+    touched = min(E, batch * top)
+    out["malulorn", "decode", "moe_gate_up"] = ("hbm", touched * 2 * eff * D * 2)
+    out["malulorn", "decode", "moe_down"] = ("hbm", touched * eff * D * 2)
+    out["malulorn", "decode", "moe_gate_up_mma"] = ("hbm", touched * 2 * eff * D * 2)
+    out["malulorn", "decode", "moe_down_mma"] = ("hbm", touched * eff * D * 2)
+    for kind, n in (("prefill", tokens), ("decode", batch)):
+        out["malulorn", kind, "moe_route"] = ("hbm", n * D * 2 + E * D * 4)
+        out["malulorn", kind, "moe_combine"] = ("hbm", n * D * (top * 4 + 2 + 2))
+        out["malulorn", kind, "layernorm"] = ("hbm", n * D * (4 + 4 + 2 + 2))
+        out["llama", kind, "rmsnorm"] = ("hbm", n * D * (4 + 4 + 2 + 2))
+        out["malulorn", kind, "heads_gate"] = ("hbm", n * H * d * 4)
+    return out
+
+
 def llama_like_config(size):
     import cpp_minilamma_b200 as ml
     s = DESIGN_SIZES[size]
@@ -495,8 +553,8 @@ def design_rooflines(size, tokens, batch, context, peaks):
 
 
 def bench_design(args):
-    """Prompt and decode throughput of the Kupirax decoder and of the Llama decoder at equal width, feed-forward,
-    heads and layer count (random bfloat16 weights), and the device time of each of this library's kernels in one
+    """Prompt and decode throughput of the Kupirax or Malulorn decoder and of the Llama decoder at equal width,
+    feed-forward, heads and layer count (random bfloat16 weights), and the device time of each of this library's kernels in one
     prompt step and one decode step of either, with the fraction of the measured peak it reaches."""
     import numpy as np
     import torch
@@ -505,14 +563,17 @@ def bench_design(args):
     peaks = load_peaks()
     warmup, steps = max(args.warmup, 3), max(min(args.steps, 64), 8)
     tokens, batch, context = PREFILL_TOKENS, 64, 1024
-    result = {"design": "kupirax", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+    design = args.design
+    make_config = {"kupirax": kupirax_config, "malulorn": malulorn_config}[design]
+    rooflines = {"kupirax": design_rooflines, "malulorn": malulorn_rooflines}[design]
+    result = {"design": design, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
               "prefill_tokens": tokens, "decode_prompts": "uniform[128,1024)", "steps": steps, "warmup": warmup,
               "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": peaks["source"]},
               "sizes": {}}
     for size in ([args.size] if args.size else list(DESIGN_SIZES)):
         entry = {}
-        expected = design_rooflines(size, tokens, batch, context, peaks)
-        for model, cfg in (("kupirax", kupirax_config(size)), ("llama", llama_like_config(size))):
+        expected = rooflines(size, tokens, batch, context, peaks)
+        for model, cfg in ((design, make_config(size)), ("llama", llama_like_config(size))):
             llm = ml.random_model(cfg, seed=0, dtype="bfloat16", max_tokens=batch * 1536 + 8192, max_positions=4096,
                                   max_seqs=batch, max_step_tokens=8192)
             numbers = {"layers": len(llm.model.spec.schedule), "parameters": llm.model.parameter_count()}
@@ -573,7 +634,7 @@ def main():
     parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31_8b", help="model shape of the --profile step")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode step")
     parser.add_argument("--context", type=int, default=1024, help="prompt length of the --profile decode step")
-    parser.add_argument("--design", choices=["kupirax"], default=None,
+    parser.add_argument("--design", choices=["kupirax", "malulorn"], default=None,
                         help="instead of the default workload: prompt and decode throughput and kernel times of that "
                              "decoder beside the Llama decoder at equal sizes")
     parser.add_argument("--size", choices=sorted(DESIGN_SIZES), default=None, help="one size of --design (default: all)")

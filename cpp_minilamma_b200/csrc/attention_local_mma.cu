@@ -4,6 +4,11 @@
 // The kernel is instantiated for padded sizes DK, DV in {32, 64, 128, 256}; the real d and dv (multiples of
 // 8, so that rows are whole 16-byte words) are runtime values and the padding columns are zero-filled in
 // shared memory.  A tile starts at the first page that its first row's chunk (or window) reaches.
+//
+// The same kernel serves steps of single tokens (`heads_as_rows`): a block then takes one sequence and one kv head,
+// and its rows are the query heads of that kv head's group (up to 64 a block), all at the sequence's last
+// position - few rows of a 16-row tensor-core tile when the group is small, a full tile when many heads share one
+// key/value head (attention over a latent).  One block walks the whole context; there are no context splits.
 #include "attention_decode.cuh"
 #include "common.cuh"
 
@@ -24,6 +29,7 @@ struct LocalMmaArgs {
   int n_heads, n_kv_heads, max_blocks, window, chunk, d, dv;
   float scale_log2;
   int sink;                      // 1: one more term exp(0) in the softmax's denominator, without a value
+  int heads_as_rows;             // 1: single tokens; grid (sequences, kv heads * chunks of 64 heads of a group)
   int v_ld;                      // elements between value rows: dv, or d when the values are the keys' leading columns
 };
 
@@ -45,13 +51,18 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int seq = a.tile_seq[blockIdx.x], row0 = a.tile_row0[blockIdx.x];
-  const int h = blockIdx.y;
-  const int kvh = h / (a.n_heads / a.n_kv_heads);
-  const int ctx = a.seq_ctx[seq], qlen = a.seq_qlen[seq];
-  const int rows = min(64, qlen - row0);
+  const int group = a.n_heads / a.n_kv_heads;
+  const bool by_heads = a.heads_as_rows != 0;
+  const int head_chunks = (group + 63) / 64;
+  const int seq = by_heads ? blockIdx.x : a.tile_seq[blockIdx.x], row0 = by_heads ? 0 : a.tile_row0[blockIdx.x];
+  const int kvh = by_heads ? blockIdx.y / head_chunks : blockIdx.y / group;
+  const int h = by_heads ? kvh * group + (blockIdx.y % head_chunks) * 64 : blockIdx.y;  // the (first) head of the block
+  const int ctx = a.seq_ctx[seq], qlen = by_heads ? 1 : a.seq_qlen[seq];
+  const int rows = by_heads ? min(64, kvh * group + group - h) : min(64, qlen - row0);
   const int pos0 = ctx - qlen + row0;
+  const int pos_step = by_heads ? 0 : 1;  // rows are consecutive positions, or heads at one position
   const int d = a.d, dv = a.dv;
+  const size_t q_stride = by_heads ? d : (size_t)a.n_heads * d, o_stride = by_heads ? dv : (size_t)a.n_heads * dv;
   const int* table = a.block_table + (size_t)a.seq_slot[seq] * a.max_blocks;
   constexpr int KCPR = DK / 8, VCPR = DV / 8;  // 16-byte words per padded row
 
@@ -60,7 +71,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     for (int c = tid; c < 64 * KCPR; c += 128) {
       const int r = c / KCPR, cc = c % KCPR;
       const bool in = r < rows && cc * 8 < d;
-      cp_async16_zfill(q_s + r * L::KS + cc * 8, qg + (size_t)min(r, rows - 1) * a.n_heads * d + (in ? cc * 8 : 0), in);
+      cp_async16_zfill(q_s + r * L::KS + cc * 8, qg + (size_t)min(r, rows - 1) * q_stride + (in ? cc * 8 : 0), in);
     }
   }
   auto load_page = [&](int page_index, int stage) {
@@ -84,7 +95,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
 
   int first_key = a.chunk > 0 ? (pos0 / a.chunk) * a.chunk : 0;  // of the tile's first row; later rows reach no further back
   if (a.window > 0) first_key = max(first_key, pos0 - a.window + 1);
-  const int last_pos = pos0 + rows - 1;
+  const int last_pos = pos0 + (rows - 1) * pos_step;
   const int last_chunk_start = a.chunk > 0 ? (last_pos / a.chunk) * a.chunk : 0;
   const int p_first = first_key / MLL_PAGE, p_last = last_pos / MLL_PAGE;
   load_page(p_first, 0);
@@ -133,7 +144,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
       }
     }
     // mask where the page meets the diagonal, a chunk's or the window's edge, or the tile's end
-    const bool needs_mask = (p * MLL_PAGE + MLL_PAGE - 1 > pos0 + warp * 16) || a.window > 0 || rows < 64 ||
+    const bool needs_mask = (p * MLL_PAGE + MLL_PAGE - 1 > pos0 + warp * 16 * pos_step) || a.window > 0 || rows < 64 ||
                             p * MLL_PAGE < last_chunk_start;
 #pragma unroll
     for (int n = 0; n < 8; ++n)
@@ -142,7 +153,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
         float v = s_acc[n][i] * a.scale_log2;
         if (needs_mask) {
           const int row = warp * 16 + g + ((i >> 1) << 3);
-          const int qpos = pos0 + row;
+          const int qpos = pos0 + row * pos_step;
           const int kpos = p * MLL_PAGE + n * 8 + 2 * t + (i & 1);
           const bool ok = row < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window) &&
                           (a.chunk <= 0 || kpos >= (qpos / a.chunk) * a.chunk);
@@ -206,7 +217,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     const int row = warp * 16 + g + 8 * r;
     if (row >= rows) continue;
     const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
-    __nv_bfloat16* dst = a.out + ((size_t)a.seq_qstart[seq] + row0 + row) * a.n_heads * dv + (size_t)h * dv;
+    __nv_bfloat16* dst = a.out + ((size_t)a.seq_qstart[seq] + row0) * a.n_heads * dv + (size_t)h * dv + row * o_stride;
 #pragma unroll
     for (int n = 0; n < NT_OUT; ++n)
       if (n * 8 + 2 * t < dv)  // dv is even: a pair is inside or outside as a whole
@@ -224,7 +235,9 @@ int launch_local_mma(const LocalMmaArgs& a, int n_tiles, cudaStream_t stream) {
     mll_set_error("local attention (mma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
     return (int)err;
   }
-  MLL_LAUNCH((kernel), dim3(n_tiles, a.n_heads), 128, smem, stream, a);
+  const int group = a.n_heads / a.n_kv_heads;
+  const dim3 grid(n_tiles, a.heads_as_rows ? a.n_kv_heads * ((group + 63) / 64) : a.n_heads);
+  MLL_LAUNCH((kernel), grid, 128, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -244,11 +257,12 @@ MLL_API int mll_local_attention_mma_supported(int dtype, int d, int dv) {
 }
 
 // tile_seq / tile_row0: tiles of up to 64 query rows as (sequence, first row among the sequence's new tokens).
+// heads_as_rows: every sequence brings one token; n_tiles is then the number of sequences and the lists are not read.
 MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                                     const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
                                     const int* tile_row0, const int* block_table, void* out, int n_tiles, int n_heads,
                                     int n_kv_heads, int d, int dv, int chunk, int window, int max_blocks, float scale,
-                                    int sink, int v_in_k, cudaStream_t stream) {
+                                    int sink, int v_in_k, int heads_as_rows, cudaStream_t stream) {
   MLL_REQUIRE(mll_local_attention_mma_supported(MLL_BF16, d, dv), "local attention (mma): head sizes %d / %d", d, dv);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention (mma): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_heads <= 65535 && chunk >= 0 && window >= 0, "local attention (mma): bad tile count, chunk or window");
@@ -257,7 +271,7 @@ MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const vo
   mll::LocalMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                       seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, d, dv,
-                      scale * 1.4426950408889634f, sink ? 1 : 0, v_in_k ? d : dv};
+                      scale * 1.4426950408889634f, sink ? 1 : 0, heads_as_rows ? 1 : 0, v_in_k ? d : dv};
   if (d <= 32) return mll::dispatch_local_mma_v<32>(a, n_tiles, stream);
   if (d <= 64) return mll::dispatch_local_mma_v<64>(a, n_tiles, stream);
   if (d <= 128) return mll::dispatch_local_mma_v<128>(a, n_tiles, stream);

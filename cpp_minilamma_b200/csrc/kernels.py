@@ -838,12 +838,12 @@ def attention_prefill_takes_chunks(dtype: torch.dtype, head_dim: int) -> bool:
 
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                       block_table, out, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                      window: int, scale: float, wide_tiles=None, chunk: int = 0) -> None:
+                      window: int, scale: float, wide_tiles=None, chunk: int = 0, sink: bool = False) -> None:
     """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache.
     `wide_tiles`: (sequence, first row) int32 lists of the same rows in tiles of 128, which the tcgen05 kernel
     works on; without them it walks the 64-row list and every other block finds nothing to do.
     `chunk` > 0 (the tcgen05 kernel only; ask `attention_prefill_takes_chunks` first): key j is visible from query i
-    only if j // chunk == i // chunk."""
+    only if j // chunk == i // chunk.  `sink` (the same kernel only): one more term exp(0) in the softmax's denominator."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
     for name, t in (("seq_slot", seq_slot), ("seq_ctx", seq_ctx), ("seq_qstart", seq_qstart),
                     ("seq_qlen", seq_qlen), ("tile_seq", tile_seq), ("tile_row0", tile_row0)):
@@ -866,10 +866,11 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
                                           ctypes.c_longlong(k_cache.shape[0]), ctypes.c_int(n_tiles),
                                           ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                           ctypes.c_int(block_table.shape[1]), ctypes.c_int(window), ctypes.c_int(chunk),
-                                          ctypes.c_float(scale), _stream()), "attention_prefill (tcgen05)")
+                                          ctypes.c_float(scale), ctypes.c_int(int(sink)), _stream()),
+               "attention_prefill (tcgen05)")
         return
-    if chunk:
-        raise KernelError("attention prefill: only the tcgen05 kernel masks by chunks")
+    if chunk or sink:
+        raise KernelError("attention prefill: only the tcgen05 kernel masks by chunks or has a sink")
     if USE_TENSOR_CORE_PREFILL and lib().mll_attn_prefill_mma_supported(dtype_code(q.dtype), head_dim):
         _check(lib().mll_attn_prefill_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                           _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
@@ -1021,7 +1022,27 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(tile_seq), _ptr(tile_row0), _ptr(block_table), _ptr(out), ctypes.c_int(tile_seq.shape[0]),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
-        ctypes.c_int(int(v_in_k)), _stream()), "local_attention_mma")
+        ctypes.c_int(int(v_in_k)), ctypes.c_int(0), _stream()), "local_attention_mma")
+
+
+def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, block_table, out, n_seqs: int,
+                          n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int, scale: float,
+                          sink: bool = False, v_in_k: bool = False) -> None:
+    """`local_attention` for steps in which every sequence brings one token, bfloat16, on tensor cores: a block per
+    (sequence, kv head) whose rows are the query heads of that kv head's group."""
+    _need(q, "local attention q", torch.bfloat16, 2)
+    _need(out, "local attention out", torch.bfloat16, 2)
+    _need(k_cache, "local attention k cache", torch.bfloat16, 4)
+    _need(v_cache, "local attention v cache", torch.bfloat16, 4)
+    if tuple(q.shape) != (n_seqs, n_heads * d) or tuple(out.shape) != (n_seqs, n_heads * dv):
+        raise KernelError(f"local attention: q {tuple(q.shape)} / out {tuple(out.shape)} for {n_seqs} single tokens")
+    _check_local_caches(k_cache, v_cache, n_kv_heads, d, dv, v_in_k)
+    _check(lib().mll_local_attention_mma(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx), _ptr(seq_qstart), _ptr(seq_qlen),
+        _ptr(seq_slot), _ptr(seq_slot), _ptr(block_table), _ptr(out), ctypes.c_int(n_seqs),
+        ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
+        ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
+        ctypes.c_int(int(v_in_k)), ctypes.c_int(1), _stream()), "local_attention_heads")
 
 
 # --------------------------------------------------------------------------- #

@@ -170,14 +170,22 @@ class ChunkedAttention(Mixer):
                                step.n_seqs, self.n_heads, self.n_kv_heads, self.d, 1, self.window, self.scale,
                                chunk=self.chunk)
             return
+        if step.all_decode and self._tensor_cores():
+            # single tokens that the kernels above do not take (a sink, values of another size): the tensor-core
+            # prompt kernel with a kv head's query heads as the rows of its tile
+            K.local_attention_heads(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
+                                    cache.block_table, out, step.n_seqs, self.n_heads, self.n_kv_heads, self.d, self.dv,
+                                    self.chunk, self.window, self.scale, sink=self.sink)
+            return
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
-        if tiles and not self.sink and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
+        if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
             # keys and values of one head size that the Llama attention's tcgen05 prompt kernel takes: that kernel,
             # which knows the chunk mask too
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                 tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out,
                                 tiles["tile_seq"].shape[0], self.n_heads, self.n_kv_heads, self.d, self.window,
-                                self.scale, wide_tiles=(tiles["wide_seq"], tiles["wide_row0"]), chunk=self.chunk)
+                                self.scale, wide_tiles=(tiles["wide_seq"], tiles["wide_row0"]), chunk=self.chunk,
+                                sink=self.sink)
             return
         if tiles and self._tensor_cores():
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,

@@ -133,7 +133,11 @@ class LatentAttention(Mixer):
         torch.bmm(q_plain, self.w_uk, out=q.view(T, H, self.row)[:, :, :self.rank].transpose(0, 1))
         latent = step.ws.buffer("latent.o", (T, H * self.rank), act)
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
-        if tiles and K.local_attention_mma_supported(act, self.row, self.rank):
+        if step.all_decode and K.local_attention_mma_supported(act, self.row, self.rank):
+            # single tokens: all heads read the one latent row per position, so they are the rows of one tile
+            K.local_attention_heads(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
+                                    cache.block_table, latent, T, H, 1, self.row, self.rank, 0, 0, self.scale, v_in_k=True)
+        elif tiles and K.local_attention_mma_supported(act, self.row, self.rank):
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, latent, H, 1, self.row,
                                     self.rank, 0, 0, self.scale, v_in_k=True)

@@ -363,6 +363,41 @@ def test_attention_kernels_with_a_far_key_that_stands_out(dtype, d, dv, sink, v_
         assert err <= 3e-2 * max(1.0, want.abs().max().item()), ("tensor-core kernel", err)
 
 
+@pytest.mark.parametrize("H,G,d,dv,sink,v_in_k", [(4, 2, 16, 24, True, False), (20, 1, 48, 32, False, True),
+                                                  (80, 1, 144, 128, False, True), (6, 3, 72, 136, True, False),
+                                                  (8, 8, 64, 64, True, False), (3, 1, 256, 8, True, False)])
+def test_single_token_kernel_with_heads_as_rows(H, G, d, dv, sink, v_in_k):
+    """Single tokens in bfloat16 on tensor cores, a kv head's query heads as the rows of a tile (more than 64 heads
+    take two blocks): contexts of one key, at and around page borders, and hundreds of keys with an early one that
+    stands out; against the softmax written out."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(H * 100 + d)
+    ctxs = [1, 2, 63, 64, 65, 128, 129, 300]
+    n = len(ctxs)
+    k_cache, v_cache, table = _paged(gen, ctxs, G, d, dv, torch.bfloat16, dev, v_in_k)
+    q = torch.randn((n, H * d), generator=gen).to(torch.bfloat16)
+    for s in range(n):
+        if ctxs[s] > 100:
+            mean_q = q[s].float().view(H, d).mean(dim=0)
+            k_cache[int(table[s, 0]), :, 3, :] = (k_cache[int(table[s, 0]), :, 3, :].float() + 6.0 * mean_q / mean_q.norm()).to(torch.bfloat16)
+    scale = 1.0 / d ** 0.5
+    want = torch.cat([_attention_oracle(q[s:s + 1].double().view(1, H, d), _dense(k_cache, table, s, ctxs[s], d),
+                                        _dense(v_cache, table, s, ctxs[s], dv), ctxs[s] - 1, scale, sink, H // G)
+                      for s in range(n)]).view(n, H * dv)
+    state = make_step_state(dev, list(range(n)), [c - 1 for c in ctxs], [1] * n)
+    kc = k_cache.to(dev)
+    vc = kc if v_in_k else v_cache.to(dev)
+    out = torch.zeros((n, H * dv), dtype=torch.bfloat16, device=dev)
+    K.local_attention_heads(q.to(dev), kc, vc, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
+                            table.to(dev), out, n, H, G, d, dv, 0, 0, scale, sink=sink, v_in_k=v_in_k)
+    torch.cuda.synchronize()
+    err = (out.cpu().double() - want).abs()
+    assert torch.isfinite(out.float()).all()
+    assert err.max().item() <= 3e-2 * max(1.0, want.abs().max().item()), (err.max().item(), int(err.argmax()) // (H * dv))
+
+
 @pytest.mark.parametrize("every,coef", [(1, 1.0), (5, 0.3), (64, 0.7)])
 def test_query_temperature_steps_at_the_right_positions(every, coef):
     """The prepare kernel alone: q at positions just before, at and just after every step of the temperature."""

@@ -52,7 +52,7 @@ CONFIGS = {
                              latent(heads=4, dim=8, rot_dim=16, vdim=24, kv_rank=24, base=10000.0, mlp=moe(3, 1, 32, 8))],
                             width=56, vocab=131, eps=1e-6, loop=(1, 3, 2)),
     # heads of one, one expert per token, every expert per token, a single expert, a loop of one pass, a dense layer
-    "ones": lambda: config([attention(heads=1, kv_heads=1, dim=32, vdim=16, temp=(1.0, 1), mlp=moe(4, 1, 16, 8)),
+    "ones": lambda: config([attention(heads=1, kv_heads=1, dim=32, vdim=16, temp=(0.5, 1), mlp=moe(4, 1, 16, 8)),
                             latent(heads=1, dim=40, rot_dim=2, vdim=40, kv_rank=8, mlp=moe(3, 3, 8, 0)),
                             attention(heads=2, kv_heads=1, dim=8, vdim=8, temp=None, mlp=moe(1, 1, 24, 24)),
                             latent(heads=2, dim=8, rot_dim=8, vdim=4, kv_rank=72, mlp={"kind": "dense", "ff": 24})],
@@ -130,7 +130,7 @@ def make_weights(cfg, seed):
         elif leaf == "mlp.router":
             a = 2.0 * rng.randn(*shape) / np.sqrt(fan_in)
         elif leaf == "mix.q":
-            a = 3.0 * rng.randn(*shape) / np.sqrt(fan_in)
+            a = 2.0 * rng.randn(*shape) / np.sqrt(fan_in)
         elif name in ("embed", "loop.step"):
             a = rng.randn(*shape)
         elif name == "loop.in":
