@@ -37,6 +37,9 @@ struct DecodeMmaArgs {
   // entry says (at most n_splits, which stays the stride of the partial results), long sequences more than
   // short ones.
   const int* work;
+  // 1: the softmax's denominator has one more term exp(0) that carries no value (a sink); it is counted once, by the
+  // block that holds a sequence's first keys
+  int sink;
 };
 
 __device__ __forceinline__ float2 unpack_bf162(unsigned r) {

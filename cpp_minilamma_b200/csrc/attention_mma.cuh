@@ -95,6 +95,10 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8
+  if (a.sink && split == 0) {  // the sink: as if one key that scores 0 and has no value had been seen
+    m_run[0] = m_run[1] = 0.f;
+    l_run[0] = l_run[1] = 1.f;
+  }
 
   const int n_pages = max(0, p_end - p_begin);
 #pragma unroll

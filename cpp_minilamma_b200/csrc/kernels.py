@@ -640,8 +640,9 @@ USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
                      scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None,
-                     work: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+                     work: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
+    `sink` (bfloat16 tensor-core kernels only): one more term exp(0) in the softmax's denominator.
     `chunk` > 0 (not together with a window): the query sees the keys of its own chunk of that many positions only,
     chunks counted from position 0; the kernels take it as a negative window.
     bfloat16 runs on tensor cores (head sizes 16 .. 256 in steps of 16), float32 on the general kernel.
@@ -669,7 +670,8 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
     if q.dtype == torch.bfloat16 and _tma_decode(q, None, None, None, False, False, k_cache, v_cache, seq_slot, seq_ctx,
                                                 block_table, scratch, out, n_seqs, n_heads, n_kv_heads, head_dim,
-                                                n_splits, window, scale, counters, _order(order, n_seqs), work):
+                                                n_splits, window, scale, counters, _order(order, n_seqs), work,
+                                                sink=sink):
         return
     if work is not None:
         raise KernelError("attention decode: a work list was given, but the kernel that takes one does not run here")
@@ -679,13 +681,15 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                                          ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits),
                                          ctypes.c_int(window), ctypes.c_float(scale),
-                                         _ptr(counters if n_splits > 1 else None), _stream()),
+                                         _ptr(counters if n_splits > 1 else None), ctypes.c_int(int(sink)), _stream()),
                "attention_decode (tensor cores)")
         if n_splits > 1 and counters is None:
             _check(lib().mll_attn_combine(_ptr(scratch), _ptr(out), code, ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
                                           ctypes.c_int(head_dim), ctypes.c_int(n_splits), _stream()),
                    "attention_combine")
         return
+    if sink:
+        raise KernelError("attention decode: only the tensor-core kernels have a sink")
     _check(lib().mll_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                  _ptr(block_table), _ptr(scratch), _ptr(out), code,
                                  ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
@@ -726,7 +730,8 @@ def _work(work, n_seqs: int, n_splits: int):
 
 
 def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
-                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None, work=None) -> bool:
+                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None, work=None,
+                sink: bool = False) -> bool:
     """Runs the TMA-fed decode kernel when it takes the problem (bfloat16, head_dim 64/128, arrival
     counters whenever the context is split); returns whether it did."""
     if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_tma_supported(dtype_code(out.dtype), head_dim)):
@@ -742,7 +747,8 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits), ctypes.c_int(window),
                                      ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
                                      ctypes.c_int(int(USE_CLUSTER_MERGE)), _ptr(order), _ptr(work),
-                                     ctypes.c_int(work.shape[0] if work is not None else 0), _stream()),
+                                     ctypes.c_int(work.shape[0] if work is not None else 0), ctypes.c_int(int(sink)),
+                                     _stream()),
            "attention_decode (TMA, work list)" if work is not None
            else "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
            else "attention_decode (TMA)")
@@ -1231,9 +1237,10 @@ def moe_max_tiles(n_pairs: int, n_experts: int, rows: int) -> int:
     return n_pairs // rows + n_experts
 
 
-def moe_route(h, w, bias, chosen, weight, top: int) -> None:
+def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tensor] = None) -> None:
     """chosen [T, top] (int32) = the experts with the largest z = w h + bias (float32; ties: the lower index),
-    weight [T, top] (float32) = softmax over the chosen logits."""
+    weight [T, top] (float32) = softmax over the chosen logits.  `logits`: float32 [T, E] = h w^T when the caller
+    has formed the product already (a library product over many tokens)."""
     _need(h, "moe route h", None, 2)
     _need(w, "moe route weight", torch.float32, 2)
     _need(chosen, "moe route chosen", torch.int32, 2)
@@ -1246,7 +1253,11 @@ def moe_route(h, w, bias, chosen, weight, top: int) -> None:
         _need(bias, "moe route bias", torch.float32, 1)
         if bias.shape[0] != experts:
             raise KernelError("moe route: one bias per expert is needed")
-    _check(lib().mll_moe_route(_ptr(h), _ptr(w), _ptr(bias), _ptr(chosen), _ptr(weight), dtype_code(h.dtype),
+    if logits is not None:
+        _need(logits, "moe route logits", torch.float32, 2)
+        if tuple(logits.shape) != (n, experts):
+            raise KernelError(f"moe route: logits {tuple(logits.shape)}, expected {(n, experts)}")
+    _check(lib().mll_moe_route(_ptr(h), _ptr(w), _ptr(bias), _ptr(logits), _ptr(chosen), _ptr(weight), dtype_code(h.dtype),
                                ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(experts), ctypes.c_int(top), _stream()),
            "moe_route")
 

@@ -8,7 +8,8 @@
 // sized for the most tiles there can be (pairs / MOE_BM + E), blocks past the real count leaving at once.  So a
 // step's launches depend on its number of tokens alone and a decode step can be captured in a graph.
 //
-//   route      a warp per token: E dot products in float32, `top` rounds of a warp-wide arg-max, softmax
+//   route      a block per token: its eight warps share the E dot products (float32; for many tokens the logits
+//              come from a library product instead), then `top` rounds of a warp-wide arg-max and the softmax
 //   sort       one block: counts per expert, their running sums, the tile list, the pairs' places
 //   gate_up    tile x 128 activation columns: act[place, n] = silu(gate) * up, rows gathered by token
 //   down       tile x 128 output columns: y[pair, :] = weight * (W_down act[place]), float32
@@ -16,7 +17,8 @@
 //
 // The products here are the plain form (a thread per output column, the tile's rows in shared memory, float32
 // accumulation in k order); every weight of an expert is read once per tile, which is what a decode step needs.
-// bfloat16 steps with many rows per expert take the tensor-core kernels of moe_mma.cu for the two products.
+// They serve float32 and sizes whose rows are no whole 16-byte words; bfloat16 steps take the tensor-core kernels of
+// moe_mma.cu for the two products.
 #include "common.cuh"
 #include "moe.cuh"
 
@@ -24,24 +26,32 @@ namespace mll {
 
 // ---- route ---------------------------------------------------------------------------------------------------- //
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w,
-                                                        const float* __restrict__ bias, int* __restrict__ chosen,
-                                                        float* __restrict__ weight, int n_tokens, int width,
-                                                        int n_experts, int top) {
-  extern __shared__ float z_all[];
+__global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                                                        const float* __restrict__ bias, const float* __restrict__ logits,
+                                                        int* __restrict__ chosen, float* __restrict__ weight,
+                                                        int n_tokens, int width, int n_experts, int top) {
+  extern __shared__ float z[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= n_tokens) return;
-  float* z = z_all + (size_t)warp * n_experts;
-  const T* row = h + (size_t)t * width;
-  for (int e = 0; e < n_experts; ++e) {
-    const float* we = w + (size_t)e * width;
-    float s = 0.f;
-    for (int i = lane; i < width; i += 32) s = fmaf(to_float(row[i]), we[i], s);
-    s = warp_sum(s);
-    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  const int t = blockIdx.x;
+  if (logits) {  // w h was formed elsewhere
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) z[e] = logits[(size_t)t * n_experts + e] + (bias ? bias[e] : 0.f);
+  } else {
+    const T* row = h + (size_t)t * width;
+    for (int e = warp; e < n_experts; e += 8) {
+      const float* we = w + (size_t)e * width;
+      float s[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums a lane: the loads of a round are in flight together
+      int i = lane;
+      for (; i + 96 < width; i += 128) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) s[u] = fmaf(to_float(row[i + 32 * u]), we[i + 32 * u], s[u]);
+      }
+      for (; i < width; i += 32) s[0] = fmaf(to_float(row[i]), we[i], s[0]);
+      const float total = warp_sum((s[0] + s[1]) + (s[2] + s[3]));
+      if (lane == 0) z[e] = total + (bias ? bias[e] : 0.f);
+    }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float first = 0.f, total = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -216,21 +226,22 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
 MLL_API int mll_moe_simt_rows() { return MOE_SIMT_BM; }
 
 // h: [n_tokens, width] of `dtype`; w: float32 [n_experts, width]; bias: float32 [n_experts] or null;
+// logits: null, or float32 [n_tokens, n_experts] = h w^T formed by the caller (h and w are then not read);
 // chosen: int32 [n_tokens, top]; weight: float32 [n_tokens, top].
-MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, int* chosen, float* weight, int dtype,
-                          int n_tokens, int width, int n_experts, int top, cudaStream_t stream) {
+MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, const float* logits, int* chosen,
+                          float* weight, int dtype, int n_tokens, int width, int n_experts, int top,
+                          cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
               "moe route: bad sizes tokens=%d width=%d experts=%d top=%d", n_tokens, width, n_experts, top);
   MLL_REQUIRE(n_experts <= 2048, "moe route: %d experts (at most 2048)", n_experts);
   if (n_tokens == 0) return 0;
-  const size_t smem = (size_t)4 * n_experts * sizeof(float);
-  const int blocks = (n_tokens + 3) / 4;
+  const size_t smem = (size_t)n_experts * sizeof(float);
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::moe_route_kernel<float>), blocks, 128, smem, stream, (const float*)h, w, bias, chosen, weight,
-               n_tokens, width, n_experts, top);
+    MLL_LAUNCH((mll::moe_route_kernel<float>), n_tokens, 256, smem, stream, (const float*)h, w, bias, logits, chosen,
+               weight, n_tokens, width, n_experts, top);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::moe_route_kernel<__nv_bfloat16>), blocks, 128, smem, stream, (const __nv_bfloat16*)h, w, bias,
-               chosen, weight, n_tokens, width, n_experts, top);
+    MLL_LAUNCH((mll::moe_route_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)h, w, bias,
+               logits, chosen, weight, n_tokens, width, n_experts, top);
   else
     MLL_REQUIRE(false, "moe route: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

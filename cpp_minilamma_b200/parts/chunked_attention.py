@@ -162,13 +162,14 @@ class ChunkedAttention(Mixer):
 
     def _attend(self, step, q, cache, out) -> None:
         act = self.ctx.act_dtype
-        if (not self.sink and step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
-                and not (self.chunk and self.window) and act == torch.bfloat16):
+        if (step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+                and not (self.chunk and self.window) and act == torch.bfloat16
+                and (not self.sink or K.USE_TENSOR_CORE_DECODE)):
             # single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed or
             # mma.sync), which take the chunk as the key range's start; one block per (sequence, kv head)
             K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, None, out,
                                step.n_seqs, self.n_heads, self.n_kv_heads, self.d, 1, self.window, self.scale,
-                               chunk=self.chunk)
+                               chunk=self.chunk, sink=self.sink)
             return
         if step.all_decode and self._tensor_cores():
             # single tokens that the kernels above do not take (a sink, values of another size): the tensor-core

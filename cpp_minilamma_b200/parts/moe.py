@@ -8,7 +8,7 @@
 The experts' matrices are stacked ([E, 2 I, D] gate rows then up rows, and [E, D, I]); the routing stays on the
 device: the (token, choice) pairs are sorted by expert there and the two products run over tiles of one expert's
 rows (csrc/moe.cu), so a step's launches follow from its number of tokens alone and decode steps replay from a
-graph.  bfloat16 steps with enough rows per expert take the tensor-core kernels.  The shared expert is a dense
+graph.  bfloat16 steps take the tensor-core kernels, float32 steps the plain ones.  The shared expert is a dense
 SwiGLU feed-forward of its own width (the `swiglu` part); its output is added in the same pass that sums a token's
 experts.
 """
@@ -32,6 +32,7 @@ class RoutedFeedForward(FeedForward):
     """
 
     capturable = True
+    ROUTE_BY_PRODUCT = 256  # tokens from which the router's logits are a library product
 
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
@@ -98,9 +99,21 @@ class RoutedFeedForward(FeedForward):
         n_pairs = T * self.top
         chosen = ws.buffer("moe.chosen", (T, self.top), torch.int32)
         weight = ws.buffer("moe.weight", (T, self.top), torch.float32)
-        K.moe_route(h, self.router, self.router_bias, chosen, weight, self.top)
-        # tensor cores pay once an expert's tiles fill: with few rows per expert every weight is read for a handful of rows
-        mma = (n_pairs >= 8 * self.experts and K.USE_TENSOR_CORE_MOE and K.moe_mma_supported(act, D, self.inter))
+        logits = None
+        if T > self.ROUTE_BY_PRODUCT:
+            # many tokens: the logits as one library product in float32 (the rows widened first); few: in the kernel
+            if torch.backends.cuda.matmul.allow_tf32:
+                raise RuntimeError("routed feed-forward: TF32 is enabled; the router's logits need true 32-bit products")
+            wide = h
+            if h.dtype != torch.float32:
+                wide = ws.buffer("moe.h32", (T, D), torch.float32)
+                K.cast(h, wide)
+            logits = ws.buffer("moe.logits", (T, self.experts), torch.float32)
+            torch.mm(wide, self.router.t(), out=logits)
+        K.moe_route(h, self.router, self.router_bias, chosen, weight, self.top, logits=logits)
+        # bfloat16: tiles of 64 rows on tensor cores at every size - with few rows per expert the products stream each
+        # touched expert's weights once, and a mostly empty tile costs nothing that memory does not hide
+        mma = K.USE_TENSOR_CORE_MOE and K.moe_mma_supported(act, D, self.inter)
         plan = self._plan(step, n_pairs, mma)
         K.moe_sort(chosen, plan, self.experts)
         hidden = ws.buffer("moe.act", (n_pairs, self.inter), act)
