@@ -8,7 +8,9 @@
 // The same kernel serves steps of single tokens (`heads_as_rows`): a block then takes one sequence and one kv head,
 // and its rows are the query heads of that kv head's group (up to 64 a block), all at the sequence's last
 // position - few rows of a 16-row tensor-core tile when the group is small, a full tile when many heads share one
-// key/value head (attention over a latent).  One block walks the whole context; there are no context splits.
+// key/value head (attention over a latent).  The context may be cut into n_splits runs of pages, a block each
+// (grid z): the blocks then leave their unnormalised results with their maxima and sums in scratch memory and a
+// second kernel merges them in split order; a sink is counted by the split that holds the first keys.
 #include "attention_decode.cuh"
 #include "common.cuh"
 
@@ -31,6 +33,9 @@ struct LocalMmaArgs {
   int sink;                      // 1: one more term exp(0) in the softmax's denominator, without a value
   int heads_as_rows;             // 1: single tokens; grid (sequences, kv heads * chunks of 64 heads of a group)
   int v_ld;                      // elements between value rows: dv, or d when the values are the keys' leading columns
+  int n_splits;                  // heads_as_rows only: blocks per (sequence, kv head, head chunk) along the context
+  float* part_o;                 // [sequences, heads, n_splits, dv] unnormalised results (n_splits > 1)
+  float* part_ml;                // [sequences, heads, n_splits, 2] maximum (log2 units) and sum
 };
 
 template <int DK, int DV>
@@ -98,7 +103,13 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   const int last_pos = pos0 + (rows - 1) * pos_step;
   const int last_chunk_start = a.chunk > 0 ? (last_pos / a.chunk) * a.chunk : 0;
   const int p_first = first_key / MLL_PAGE, p_last = last_pos / MLL_PAGE;
-  load_page(p_first, 0);
+  int pb = p_first, pe = p_last;  // this block's run of pages
+  if (a.n_splits > 1) {
+    const int per = (p_last - p_first + a.n_splits) / a.n_splits;
+    pb = p_first + (int)blockIdx.z * per;
+    pe = min(p_last, pb + per - 1);
+  }
+  if (pb <= pe) load_page(pb, 0);
   cp_async_commit();
 
   unsigned qf[KSTEPS][4];
@@ -108,20 +119,21 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
   // with a sink every row starts as if it had seen one key that scores 0 and has no value
-  float m_run[2] = {a.sink ? 0.f : -INFINITY, a.sink ? 0.f : -INFINITY}, l_run[2] = {a.sink ? 1.f : 0.f, a.sink ? 1.f : 0.f};
+  const bool sink = a.sink && (a.n_splits <= 1 || blockIdx.z == 0);
+  float m_run[2] = {sink ? 0.f : -INFINITY, sink ? 0.f : -INFINITY}, l_run[2] = {sink ? 1.f : 0.f, sink ? 1.f : 0.f};
 
-  for (int p = p_first; p <= p_last; ++p) {
-    const int stage = (p - p_first) & 1;
+  for (int p = pb; p <= pe; ++p) {
+    const int stage = (p - pb) & 1;
     cp_async_wait<0>();
     __syncthreads();
-    if (p == p_first) {
+    if (p == pb) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
         ldmatrix_x4(qf[ks], q_s + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * L::KS + ks * 16 +
                                 ((lane >> 4) << 3));
       __syncthreads();
     }
-    if (p < p_last) load_page(p + 1, stage ^ 1);
+    if (p < pe) load_page(p + 1, stage ^ 1);
     cp_async_commit();
     const __nv_bfloat16* kt = kv_s + (size_t)stage * (L::KTILE + L::VTILE);
     const __nv_bfloat16* vt = kt + L::KTILE;
@@ -216,6 +228,18 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   for (int r = 0; r < 2; ++r) {
     const int row = warp * 16 + g + 8 * r;
     if (row >= rows) continue;
+    if (a.n_splits > 1) {
+      const size_t at = (((size_t)seq * a.n_heads + h + row) * a.n_splits + blockIdx.z);
+#pragma unroll
+      for (int n = 0; n < NT_OUT; ++n)
+        if (n * 8 + 2 * t < dv)
+          *reinterpret_cast<float2*>(a.part_o + at * dv + n * 8 + 2 * t) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+      if (t == 0) {
+        a.part_ml[at * 2] = m_run[r];
+        a.part_ml[at * 2 + 1] = l_run[r];
+      }
+      continue;
+    }
     const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
     __nv_bfloat16* dst = a.out + ((size_t)a.seq_qstart[seq] + row0) * a.n_heads * dv + (size_t)h * dv + row * o_stride;
 #pragma unroll
@@ -223,6 +247,29 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
       if (n * 8 + 2 * t < dv)  // dv is even: a pair is inside or outside as a whole
         *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + 2 * t) =
             __floats2bfloat162_rn(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+  }
+}
+
+// out[seq, head, :] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m) over the splits of a single-token step, in split order.
+__global__ void local_mma_merge_kernel(LocalMmaArgs a) {
+  const int seq = blockIdx.x / a.n_heads, head = blockIdx.x % a.n_heads;
+  const size_t at = ((size_t)seq * a.n_heads + head) * a.n_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < a.n_splits; ++s) m = fmaxf(m, a.part_ml[(at + s) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < a.n_splits; ++s) {
+    const float ms = a.part_ml[(at + s) * 2];
+    if (ms > -INFINITY) l += a.part_ml[(at + s) * 2 + 1] * exp2f(ms - m);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __nv_bfloat16* dst = a.out + (size_t)a.seq_qstart[seq] * a.n_heads * a.dv + (size_t)head * a.dv;
+  for (int c = threadIdx.x; c < a.dv; c += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < a.n_splits; ++s) {
+      const float ms = a.part_ml[(at + s) * 2];
+      if (ms > -INFINITY) v += a.part_o[(at + s) * a.dv + c] * exp2f(ms - m);
+    }
+    dst[c] = __float2bfloat16_rn(v * inv);
   }
 }
 
@@ -236,9 +283,13 @@ int launch_local_mma(const LocalMmaArgs& a, int n_tiles, cudaStream_t stream) {
     return (int)err;
   }
   const int group = a.n_heads / a.n_kv_heads;
-  const dim3 grid(n_tiles, a.heads_as_rows ? a.n_kv_heads * ((group + 63) / 64) : a.n_heads);
+  const dim3 grid(n_tiles, a.heads_as_rows ? a.n_kv_heads * ((group + 63) / 64) : a.n_heads, a.n_splits);
   MLL_LAUNCH((kernel), grid, 128, smem, stream, a);
   MLL_LAUNCH_CHECK();
+  if (a.n_splits > 1) {
+    MLL_LAUNCH((local_mma_merge_kernel), n_tiles * a.n_heads, 64, 0, stream, a);
+    MLL_LAUNCH_CHECK();
+  }
   return 0;
 }
 
@@ -257,21 +308,27 @@ MLL_API int mll_local_attention_mma_supported(int dtype, int d, int dv) {
 }
 
 // tile_seq / tile_row0: tiles of up to 64 query rows as (sequence, first row among the sequence's new tokens).
-// heads_as_rows: every sequence brings one token; n_tiles is then the number of sequences and the lists are not read.
+// heads_as_rows: every sequence brings one token; n_tiles is then the number of sequences and the lists are not read;
+// n_splits > 1 cuts every context into that many runs of pages and needs scratch: n_tiles * n_heads * n_splits *
+// (dv + 2) floats.
 MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                                     const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
                                     const int* tile_row0, const int* block_table, void* out, int n_tiles, int n_heads,
                                     int n_kv_heads, int d, int dv, int chunk, int window, int max_blocks, float scale,
-                                    int sink, int v_in_k, int heads_as_rows, cudaStream_t stream) {
+                                    int sink, int v_in_k, int heads_as_rows, int n_splits, float* scratch,
+                                    cudaStream_t stream) {
   MLL_REQUIRE(mll_local_attention_mma_supported(MLL_BF16, d, dv), "local attention (mma): head sizes %d / %d", d, dv);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention (mma): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_heads <= 65535 && chunk >= 0 && window >= 0, "local attention (mma): bad tile count, chunk or window");
   MLL_REQUIRE(!v_in_k || dv <= d, "local attention (mma): values of %d cannot be the leading columns of keys of %d", dv, d);
+  MLL_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (heads_as_rows && scratch != nullptr)),
+              "local attention (mma): %d context splits need single tokens and scratch memory", n_splits);
   if (n_tiles == 0) return 0;
   mll::LocalMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                       seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, d, dv,
-                      scale * 1.4426950408889634f, sink ? 1 : 0, heads_as_rows ? 1 : 0, v_in_k ? d : dv};
+                      scale * 1.4426950408889634f, sink ? 1 : 0, heads_as_rows ? 1 : 0, v_in_k ? d : dv, n_splits,
+                      scratch, scratch ? scratch + (size_t)n_tiles * n_heads * n_splits * dv : nullptr};
   if (d <= 32) return mll::dispatch_local_mma_v<32>(a, n_tiles, stream);
   if (d <= 64) return mll::dispatch_local_mma_v<64>(a, n_tiles, stream);
   if (d <= 128) return mll::dispatch_local_mma_v<128>(a, n_tiles, stream);

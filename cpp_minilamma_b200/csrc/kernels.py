@@ -1028,14 +1028,20 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(tile_seq), _ptr(tile_row0), _ptr(block_table), _ptr(out), ctypes.c_int(tile_seq.shape[0]),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
-        ctypes.c_int(int(v_in_k)), ctypes.c_int(0), _stream()), "local_attention_mma")
+        ctypes.c_int(int(v_in_k)), ctypes.c_int(0), ctypes.c_int(1), _ptr(None), _stream()), "local_attention_mma")
 
 
 def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, block_table, out, n_seqs: int,
                           n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int, scale: float,
-                          sink: bool = False, v_in_k: bool = False) -> None:
+                          sink: bool = False, v_in_k: bool = False, n_splits: int = 1,
+                          scratch: Optional[torch.Tensor] = None) -> None:
     """`local_attention` for steps in which every sequence brings one token, bfloat16, on tensor cores: a block per
-    (sequence, kv head) whose rows are the query heads of that kv head's group."""
+    (sequence, kv head) whose rows are the query heads of that kv head's group.  `n_splits` > 1: that many blocks
+    along every context and a merge; `scratch` float32 of `local_attention_heads_scratch` floats."""
+    if n_splits > 1:
+        _need(scratch, "local attention scratch", torch.float32)
+        if scratch.numel() < local_attention_heads_scratch(n_seqs, n_heads, dv, n_splits):
+            raise KernelError("local attention: scratch too small for the split count")
     _need(q, "local attention q", torch.bfloat16, 2)
     _need(out, "local attention out", torch.bfloat16, 2)
     _need(k_cache, "local attention k cache", torch.bfloat16, 4)
@@ -1048,7 +1054,19 @@ def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(seq_slot), _ptr(seq_slot), _ptr(block_table), _ptr(out), ctypes.c_int(n_seqs),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
-        ctypes.c_int(int(v_in_k)), ctypes.c_int(1), _stream()), "local_attention_heads")
+        ctypes.c_int(int(v_in_k)), ctypes.c_int(1), ctypes.c_int(n_splits), _ptr(scratch if n_splits > 1 else None),
+        _stream()), "local_attention_heads", kernels=2 if n_splits > 1 else 1)
+
+
+def local_attention_heads_scratch(n_seqs: int, n_heads: int, dv: int, n_splits: int) -> int:
+    return n_seqs * n_heads * n_splits * (dv + 2)
+
+
+def local_attention_heads_splits(n_seqs: int, blocks_per_seq: int, multiprocessors: int) -> int:
+    """Context splits of a single-token step: enough blocks for two a multiprocessor, at most 16 a sequence; a
+    function of the batch size alone, so that a captured step keeps its launch."""
+    want = -(-2 * max(multiprocessors, 1) // max(n_seqs * blocks_per_seq, 1))
+    return max(1, min(16, want))
 
 
 # --------------------------------------------------------------------------- #

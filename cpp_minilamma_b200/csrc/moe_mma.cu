@@ -1,6 +1,8 @@
 // The two products of the routed feed-forward (moe.cu) on tensor cores, bfloat16: tiles of 64 rows of one expert
-// times 128 weight rows, mma.sync m16n8k16 with float32 accumulation, operands through a three-stage cp.async
-// ring (32 columns of k a stage).  Four warps as 2 x 2: a warp owns 32 of the tile's rows.
+// times 128 weight rows, mma.sync m16n8k16 with float32 accumulation, operands through a four-stage cp.async
+// ring (64 columns of k a stage, 108 KB of shared memory: two blocks a multiprocessor keep about 80 KB of weights
+// in flight, which a decode step - every touched expert's weights streamed once - needs to fill the memory pipe).
+// Four warps as 2 x 2: a warp owns 32 of the tile's rows.
 //   gate_up  the 128 weight rows are 64 gate rows and the 64 up rows of the same activation columns; a warp's
 //            eight 8-column tiles are four of gate and the same four of up, so silu(gate) * up happens in the
 //            accumulator registers; rows are gathered from the step's tokens by (token, choice) pair.
@@ -13,14 +15,18 @@
 
 namespace mll {
 
-constexpr int MMA_BK = 32, MMA_STAGES = 3, MMA_LD = MMA_BK + 8;  // 80-byte rows: ldmatrix without bank conflicts
+constexpr int MMA_BK = 64, MMA_STAGES = 4, MMA_LD = MMA_BK + 8;  // 144-byte rows: ldmatrix without bank conflicts
+constexpr size_t MMA_SMEM = (size_t)MMA_STAGES * (MOE_MMA_BM + 128) * MMA_LD * sizeof(__nv_bfloat16);
 
 template <bool GATE_UP>
 __global__ void __launch_bounds__(128) moe_mma_kernel(MoeProductArgs a) {
   const int tile = blockIdx.x;
   if (tile >= a.plan.n_tiles[0]) return;
-  __shared__ __align__(16) __nv_bfloat16 a_s[MMA_STAGES][MOE_MMA_BM][MMA_LD];
-  __shared__ __align__(16) __nv_bfloat16 b_s[MMA_STAGES][128][MMA_LD];
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  typedef __nv_bfloat16 (*ATile)[MOE_MMA_BM][MMA_LD];
+  typedef __nv_bfloat16 (*BTile)[128][MMA_LD];
+  ATile a_s = reinterpret_cast<ATile>(moe_smem);
+  BTile b_s = reinterpret_cast<BTile>(moe_smem + (size_t)MMA_STAGES * MOE_MMA_BM * MMA_LD * sizeof(__nv_bfloat16));
   __shared__ int row_src[MOE_MMA_BM];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp >> 1, wn = warp & 1;
@@ -126,6 +132,16 @@ __global__ void __launch_bounds__(128) moe_mma_kernel(MoeProductArgs a) {
     }
 }
 
+template <bool GATE_UP>
+int moe_mma_reserve() {
+  cudaError_t err = cudaFuncSetAttribute(moe_mma_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM);
+  if (err != cudaSuccess) {
+    mll_set_error("moe (mma): cannot reserve %zu bytes of shared memory: %s", MMA_SMEM, cudaGetErrorString(err));
+    return -1;
+  }
+  return 0;
+}
+
 }  // namespace mll
 
 MLL_API int mll_moe_mma_rows() { return MOE_MMA_BM; }
@@ -140,7 +156,8 @@ MLL_API int mll_moe_gate_up_mma(const void* h, const void* w, void* act, const i
   MLL_REQUIRE((inter + 63) / 64 <= 65535, "moe gate_up (mma): %d columns are too many for one launch", inter);
   mll::MoeProductArgs a{h, w, act, nullptr, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert, (int*)tile_row0,
                                                          (int*)n_tiles}, width, inter, top};
-  MLL_LAUNCH((mll::moe_mma_kernel<true>), dim3(max_tiles, (inter + 63) / 64), 128, 0, stream, a);
+  if (mll::moe_mma_reserve<true>() != 0) return -1;
+  MLL_LAUNCH((mll::moe_mma_kernel<true>), dim3(max_tiles, (inter + 63) / 64), 128, mll::MMA_SMEM, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -152,7 +169,8 @@ MLL_API int mll_moe_down_mma(const void* act, const void* w, float* y, const flo
   MLL_REQUIRE((width + 127) / 128 <= 65535, "moe down (mma): %d columns are too many for one launch", width);
   mll::MoeProductArgs a{act, w, y, pair_weight, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert,
                                                              (int*)tile_row0, (int*)n_tiles}, inter, width, top};
-  MLL_LAUNCH((mll::moe_mma_kernel<false>), dim3(max_tiles, (width + 127) / 128), 128, 0, stream, a);
+  if (mll::moe_mma_reserve<false>() != 0) return -1;
+  MLL_LAUNCH((mll::moe_mma_kernel<false>), dim3(max_tiles, (width + 127) / 128), 128, mll::MMA_SMEM, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }

@@ -66,8 +66,10 @@ def build_malulorn_spec(config: MalulornConfig) -> ModelSpec:
                                 norms={"input": norm(prefix + "norm1"),
                                        "post_mixer": norm(prefix + "norm2", optional=layer.mlp is None)}))
     stream_ops = []
-    if config.loops:
-        stream_ops.append(PartSpec("reentry", {"passes": config.loop_times, "names": {"in": "loop.in", "step": "loop.step"}}))
+    if config.loop_times > 0:
+        # a loop over no layers is never entered; its tensors may be in the folder all the same
+        stream_ops.append(PartSpec("reentry", {"passes": config.loop_times, "names": {"in": "loop.in", "step": "loop.step"},
+                                               "optional": not config.loops}))
     schedule = [ScheduleEntry(i, enter=None if run is None else (0, run)) for i, run in config.schedule()]
     return ModelSpec(
         hidden_size=config.width, vocab_size=config.vocab, max_positions=config.max_positions,

@@ -174,9 +174,13 @@ class ChunkedAttention(Mixer):
         if step.all_decode and self._tensor_cores():
             # single tokens that the kernels above do not take (a sink, values of another size): the tensor-core
             # prompt kernel with a kv head's query heads as the rows of its tile
+            group = self.n_heads // self.n_kv_heads
+            splits = K.local_attention_heads_splits(step.n_seqs, self.n_kv_heads * -(-group // 64), self.ctx.multiprocessors)
+            scratch = step.ws.buffer("attn.parts", (K.local_attention_heads_scratch(step.n_seqs, self.n_heads, self.dv, splits),),
+                                     torch.float32) if splits > 1 else None
             K.local_attention_heads(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     cache.block_table, out, step.n_seqs, self.n_heads, self.n_kv_heads, self.d, self.dv,
-                                    self.chunk, self.window, self.scale, sink=self.sink)
+                                    self.chunk, self.window, self.scale, sink=self.sink, n_splits=splits, scratch=scratch)
             return
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
         if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):

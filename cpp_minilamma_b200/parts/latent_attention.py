@@ -135,8 +135,12 @@ class LatentAttention(Mixer):
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
         if step.all_decode and K.local_attention_mma_supported(act, self.row, self.rank):
             # single tokens: all heads read the one latent row per position, so they are the rows of one tile
+            splits = K.local_attention_heads_splits(T, -(-H // 64), self.ctx.multiprocessors)
+            scratch = step.ws.buffer("latent.parts", (K.local_attention_heads_scratch(T, H, self.rank, splits),),
+                                     torch.float32) if splits > 1 else None
             K.local_attention_heads(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
-                                    cache.block_table, latent, T, H, 1, self.row, self.rank, 0, 0, self.scale, v_in_k=True)
+                                    cache.block_table, latent, T, H, 1, self.row, self.rank, 0, 0, self.scale, v_in_k=True,
+                                    n_splits=splits, scratch=scratch)
         elif tiles and K.local_attention_mma_supported(act, self.row, self.rank):
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, latent, H, 1, self.row,

@@ -19,7 +19,8 @@ from .linear import Linear
 
 
 class Reentry(StreamOp):
-    """params: passes, names {"in": tensor name of W_in, "step": tensor name of the per-pass vectors}."""
+    """params: passes, names {"in": tensor name of W_in, "step": tensor name of the per-pass vectors}, optional (True:
+    a folder may leave the tensors out - a model whose stretch is empty never enters it)."""
 
     capturable = True
 
@@ -27,13 +28,14 @@ class Reentry(StreamOp):
         super().__init__(params, ctx)
         self.passes = int(params["passes"])
         self.names = dict(params["names"])
+        self.optional = bool(params.get("optional", False))
         self.linear: Optional[Linear] = None
         self.step_vectors: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
         D = self.ctx.hidden_size
-        return [WeightSpec(self.names["in"], (D, 2 * D)),
-                WeightSpec(self.names["step"], (self.passes, D), kind="vector", init="normal")]
+        return [WeightSpec(self.names["in"], (D, 2 * D), optional=self.optional),
+                WeightSpec(self.names["step"], (self.passes, D), kind="vector", init="normal", optional=self.optional)]
 
     def bind(self, store) -> None:
         self.linear = Linear(store.take(self.names["in"]), self.names["in"])

@@ -389,13 +389,16 @@ def test_single_token_kernel_with_heads_as_rows(H, G, d, dv, sink, v_in_k):
     state = make_step_state(dev, list(range(n)), [c - 1 for c in ctxs], [1] * n)
     kc = k_cache.to(dev)
     vc = kc if v_in_k else v_cache.to(dev)
-    out = torch.zeros((n, H * dv), dtype=torch.bfloat16, device=dev)
-    K.local_attention_heads(q.to(dev), kc, vc, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
-                            table.to(dev), out, n, H, G, d, dv, 0, 0, scale, sink=sink, v_in_k=v_in_k)
-    torch.cuda.synchronize()
-    err = (out.cpu().double() - want).abs()
-    assert torch.isfinite(out.float()).all()
-    assert err.max().item() <= 3e-2 * max(1.0, want.abs().max().item()), (err.max().item(), int(err.argmax()) // (H * dv))
+    for splits in (1, 3, 16):  # along the context: more splits than some contexts have pages
+        out = torch.zeros((n, H * dv), dtype=torch.bfloat16, device=dev)
+        scratch = torch.full((K.local_attention_heads_scratch(n, H, dv, splits),), float("nan"), device=dev)
+        K.local_attention_heads(q.to(dev), kc, vc, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
+                                table.to(dev), out, n, H, G, d, dv, 0, 0, scale, sink=sink, v_in_k=v_in_k, n_splits=splits,
+                                scratch=scratch if splits > 1 else None)
+        torch.cuda.synchronize()
+        err = (out.cpu().double() - want).abs()
+        assert torch.isfinite(out.float()).all()
+        assert err.max().item() <= 3e-2 * max(1.0, want.abs().max().item()), (splits, err.max().item(), int(err.argmax()) // (H * dv))
 
 
 @pytest.mark.parametrize("every,coef", [(1, 1.0), (5, 0.3), (64, 0.7)])

@@ -132,3 +132,23 @@ def test_oracle_forward_shapes_and_layer_trace():
     assert logits.shape == (20, raw["vocab"]) and after.shape == (6, 20, raw["width"])
     # causal: a prefix gives the same logits
     assert np.abs(pm.forward(raw, W, toks[:9]) - logits[:9]).max() < 1e-9
+
+
+def test_command_line_random_then_inspect(tmp_path, capsys):
+    """`random` writes a folder from a configuration file (every tensor of the list, bfloat16), `inspect` reads it
+    back, and the oracle can run it."""
+    from cpp_minilamma_b200.cli import main
+    raw = tm.CONFIGS["mixed"]()
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps(raw))
+    assert main(["random", str(tmp_path / "m"), "--config", str(cfg), "--seed", "3"]) == 0
+    assert main(["inspect", str(tmp_path / "m")]) == 0
+    out = capsys.readouterr().out
+    assert "architecture: Malulorn" in out and "status=ok" in out
+    assert "tensor l1.mlp.e6.down [56, 16] bfloat16" in out and "tensor loop.step [2, 56] bfloat16" in out
+    assert "tensor l3.mix.dkv.norm [24] bfloat16" in out
+    config, W = pm.read_folder(tmp_path / "m")
+    # a layer without a feed-forward: the folder holds its second norm all the same (ones and zeros would do)
+    assert set(W) - set(tm.tensor_shapes(raw)) == {"l2.norm2", "l2.norm2.b"}
+    logits = pm.forward(config, W, tm.tokens(raw, 12, 5))
+    assert logits.shape == (12, raw["vocab"]) and np.isfinite(logits).all()
