@@ -1247,8 +1247,12 @@ class MoePlan(NamedTuple):
     mma: bool
 
 
-def moe_tile_rows(mma: bool) -> int:
-    return int(lib().mll_moe_mma_rows() if mma else lib().mll_moe_simt_rows())
+def moe_tile_rows(mma: bool, n_pairs: int = 1 << 30, n_experts: int = 1) -> int:
+    """Rows of a tile of the routed products: the plain kernels' size, or one of the tensor-core kernels' two - the
+    small one while an expert gets 16 rows or fewer on average (single tokens)."""
+    if not mma:
+        return int(lib().mll_moe_simt_rows())
+    return int(lib().mll_moe_mma_rows(ctypes.c_int(int(n_pairs <= 16 * n_experts))))
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int, rows: int) -> int:
@@ -1315,7 +1319,8 @@ def moe_gate_up(h, w, act, plan: MoePlan, top: int) -> None:
     args = (_ptr(h), _ptr(w), _ptr(act), *_plan_args(plan))
     tiles = ctypes.c_int(moe_max_tiles(n_pairs, experts, plan.rows))
     if plan.mma:
-        _check(fn(*args, tiles, ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top), _stream()), "moe_gate_up_mma")
+        _check(fn(*args, tiles, ctypes.c_int(plan.rows), ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top),
+                  _stream()), "moe_gate_up_mma")
     else:
         _check(fn(*args, dtype_code(h.dtype), tiles, ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top),
                   _stream()), "moe_gate_up")
@@ -1335,7 +1340,8 @@ def moe_down(act, w, y, pair_weight, plan: MoePlan, top: int) -> None:
     args = (_ptr(act), _ptr(w), _ptr(y), _ptr(pair_weight), *_plan_args(plan))
     tiles = ctypes.c_int(moe_max_tiles(n_pairs, experts, plan.rows))
     if plan.mma:
-        _check(fn(*args, tiles, ctypes.c_int(inter), ctypes.c_int(width), ctypes.c_int(top), _stream()), "moe_down_mma")
+        _check(fn(*args, tiles, ctypes.c_int(plan.rows), ctypes.c_int(inter), ctypes.c_int(width), ctypes.c_int(top),
+                  _stream()), "moe_down_mma")
     else:
         _check(fn(*args, dtype_code(act.dtype), tiles, ctypes.c_int(inter), ctypes.c_int(width), ctypes.c_int(top),
                   _stream()), "moe_down")

@@ -8,7 +8,7 @@
 // sized for the most tiles there can be (pairs / MOE_BM + E), blocks past the real count leaving at once.  So a
 // step's launches depend on its number of tokens alone and a decode step can be captured in a graph.
 //
-//   route      a block per token: its eight warps share the E dot products (float32; for many tokens the logits
+//   route      a block per token: its sixteen warps share the E dot products (float32; for many tokens the logits
 //              come from a library product instead), then `top` rounds of a warp-wide arg-max and the softmax
 //   sort       one block: counts per expert, their running sums, the tile list, the pairs' places
 //   gate_up    tile x 128 activation columns: act[place, n] = silu(gate) * up, rows gathered by token
@@ -26,7 +26,7 @@ namespace mll {
 
 // ---- route ---------------------------------------------------------------------------------------------------- //
 template <typename T>
-__global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w,
+__global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w,
                                                         const float* __restrict__ bias, const float* __restrict__ logits,
                                                         int* __restrict__ chosen, float* __restrict__ weight,
                                                         int n_tokens, int width, int n_experts, int top) {
@@ -37,15 +37,33 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) z[e] = logits[(size_t)t * n_experts + e] + (bias ? bias[e] : 0.f);
   } else {
     const T* row = h + (size_t)t * width;
-    for (int e = warp; e < n_experts; e += 8) {
+    const bool vec = width % 4 == 0 && ((uintptr_t)w % 16 == 0) && ((uintptr_t)h % 16 == 0);
+    for (int e = warp; e < n_experts; e += 16) {
       const float* we = w + (size_t)e * width;
-      float s[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums a lane: the loads of a round are in flight together
-      int i = lane;
-      for (; i + 96 < width; i += 128) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) s[u] = fmaf(to_float(row[i + 32 * u]), we[i + 32 * u], s[u]);
+      float s[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums a lane
+      if (vec) {
+        // 16 bytes of the weight row and four activations a lane and trip, eight trips' loads in flight together
+#pragma unroll 8
+        for (int i = lane * 4; i < width; i += 128) {
+          const float4 wv = *reinterpret_cast<const float4*>(we + i);
+          float hv[4];
+          if constexpr (sizeof(T) == 4) {
+            const float4 x = *reinterpret_cast<const float4*>(row + i);
+            hv[0] = x.x; hv[1] = x.y; hv[2] = x.z; hv[3] = x.w;
+          } else {
+            const uint2 x = *reinterpret_cast<const uint2*>(row + i);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+            hv[0] = lo.x; hv[1] = lo.y; hv[2] = hi.x; hv[3] = hi.y;
+          }
+          s[0] = fmaf(hv[0], wv.x, s[0]);
+          s[1] = fmaf(hv[1], wv.y, s[1]);
+          s[2] = fmaf(hv[2], wv.z, s[2]);
+          s[3] = fmaf(hv[3], wv.w, s[3]);
+        }
+      } else {
+        for (int i = lane; i < width; i += 32) s[0] = fmaf(to_float(row[i]), we[i], s[0]);
       }
-      for (; i < width; i += 32) s[0] = fmaf(to_float(row[i]), we[i], s[0]);
       const float total = warp_sum((s[0] + s[1]) + (s[2] + s[3]));
       if (lane == 0) z[e] = total + (bias ? bias[e] : 0.f);
     }
@@ -237,10 +255,10 @@ MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, cons
   if (n_tokens == 0) return 0;
   const size_t smem = (size_t)n_experts * sizeof(float);
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::moe_route_kernel<float>), n_tokens, 256, smem, stream, (const float*)h, w, bias, logits, chosen,
+    MLL_LAUNCH((mll::moe_route_kernel<float>), n_tokens, 512, smem, stream, (const float*)h, w, bias, logits, chosen,
                weight, n_tokens, width, n_experts, top);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::moe_route_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)h, w, bias,
+    MLL_LAUNCH((mll::moe_route_kernel<__nv_bfloat16>), n_tokens, 512, smem, stream, (const __nv_bfloat16*)h, w, bias,
                logits, chosen, weight, n_tokens, width, n_experts, top);
   else
     MLL_REQUIRE(false, "moe route: unknown dtype %d", dtype);

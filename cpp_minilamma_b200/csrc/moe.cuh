@@ -2,7 +2,6 @@
 #pragma once
 
 #define MOE_SIMT_BM 16  // rows of a tile in the plain products
-#define MOE_MMA_BM 64   // rows of a tile in the tensor-core products
 
 namespace mll {
 

@@ -85,7 +85,7 @@ class RoutedFeedForward(FeedForward):
                 + (self.shared.parameter_bytes() if self.shared is not None else 0))
 
     def _plan(self, step, n_pairs: int, mma: bool) -> K.MoePlan:
-        rows = K.moe_tile_rows(mma)
+        rows = K.moe_tile_rows(mma, n_pairs, self.experts)
         tiles = K.moe_max_tiles(n_pairs, self.experts, rows)
         ws = step.ws
         return K.MoePlan(ws.buffer("moe.order", (n_pairs,), torch.int32), ws.buffer("moe.offsets", (self.experts + 1,), torch.int32),

@@ -468,8 +468,8 @@ def test_routed_feed_forward_kernels(dtype, T, E, top, D, F):
     sure = torch.ones(T, dtype=torch.bool) if margin is None else margin > 1e-4
     assert torch.equal(chosen.cpu().long()[sure], chosen_ref[sure])
     assert (weight.cpu().double()[sure] - w_ref[sure]).abs().max().item() < 1e-5
-    for mma in ([False, True] if K.moe_mma_supported(dtype, D, F) else [False]):
-        rows = K.moe_tile_rows(mma)
+    for mma, small in ([(False, False), (True, False), (True, True)] if K.moe_mma_supported(dtype, D, F) else [(False, False)]):
+        rows = K.moe_tile_rows(mma, 1 if small else 1 << 30, 1)  # the tensor-core kernels' tiles of 128 and of 16 rows
         n_pairs = T * top
         tiles = K.moe_max_tiles(n_pairs, E, rows)
         ints = lambda n: torch.full((n,), -7, dtype=torch.int32, device=dev)
@@ -489,7 +489,7 @@ def test_routed_feed_forward_kernels(dtype, T, E, top, D, F):
         assert int(plan.n_tiles.cpu()) == sum(-(-c // rows) for c in counts)
         tol = 2e-5 if dtype == torch.float32 else 3e-2
         err = (out.cpu().double() - want)[sure].abs().max().item()
-        assert err <= tol * max(1.0, want.abs().max().item()), (mma, err)
+        assert err <= tol * max(1.0, want.abs().max().item()), (mma, small, err)
 
 
 @pytest.mark.parametrize("width", [40, 50, 256, 1000])
