@@ -51,8 +51,13 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   constexpr int KSTEPS = DK / 16;
   constexpr int NT_OUT = DV / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2 stages][K 64 x KS, V 64 x VS]
-  __nv_bfloat16* q_s = kv_s + (L::KTILE + L::VTILE);                 // the query tile passes through stage 1's K tile
+  // Values that are the keys' leading columns are read from the key tile itself: a page is loaded once and a stage
+  // is half the size (three blocks a multiprocessor instead of one at keys of 256).
+  const bool v_in_k = a.v_cache == a.k_cache;
+  const int stage_elems = v_in_k ? L::KTILE : L::KTILE + L::VTILE;
+  const int vs = v_in_k ? L::KS : L::VS;                             // elements between value rows in shared memory
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2 stages][K 64 x KS (, V 64 x VS)]
+  __nv_bfloat16* q_s = kv_s + stage_elems;                           // the query tile passes through stage 1's K tile
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -83,7 +88,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     const int page = table[page_index];
     const __nv_bfloat16* kg = a.k_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * d;
     const __nv_bfloat16* vg = a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * a.v_ld;
-    __nv_bfloat16* kd = kv_s + (size_t)stage * (L::KTILE + L::VTILE);
+    __nv_bfloat16* kd = kv_s + (size_t)stage * stage_elems;
     __nv_bfloat16* vd = kd + L::KTILE;
     const int valid_rows = ctx - page_index * MLL_PAGE;  // rows past the cached length hold no data
     for (int c = tid; c < MLL_PAGE * KCPR; c += 128) {
@@ -91,7 +96,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
       const bool in = cc * 8 < d && r < valid_rows;
       cp_async16_zfill(kd + r * L::KS + cc * 8, kg + (size_t)r * d + (in ? cc * 8 : 0), in);
     }
-    for (int c = tid; c < MLL_PAGE * VCPR; c += 128) {
+    for (int c = tid; c < (v_in_k ? 0 : MLL_PAGE * VCPR); c += 128) {
       const int r = c / VCPR, cc = c % VCPR;
       const bool in = cc * 8 < dv && r < valid_rows;
       cp_async16_zfill(vd + r * L::VS + cc * 8, vg + (size_t)r * a.v_ld + (in ? cc * 8 : 0), in);
@@ -135,8 +140,8 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     }
     if (p < pe) load_page(p + 1, stage ^ 1);
     cp_async_commit();
-    const __nv_bfloat16* kt = kv_s + (size_t)stage * (L::KTILE + L::VTILE);
-    const __nv_bfloat16* vt = kt + L::KTILE;
+    const __nv_bfloat16* kt = kv_s + (size_t)stage * stage_elems;
+    const __nv_bfloat16* vt = v_in_k ? kt : kt + L::KTILE;
 
     float s_acc[8][4];
 #pragma unroll
@@ -216,7 +221,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
         unsigned vb[4];
         const int key = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
         const int col = (n + (lane >> 4)) * 8;
-        ldmatrix_x4_trans(vb, vt + key * L::VS + col);
+        ldmatrix_x4_trans(vb, vt + key * vs + col);
         mma_16816(o[n], pa, vb[0], vb[1]);
         mma_16816(o[n + 1], pa, vb[2], vb[3]);
       }
@@ -275,7 +280,7 @@ __global__ void local_mma_merge_kernel(LocalMmaArgs a) {
 
 template <int DK, int DV>
 int launch_local_mma(const LocalMmaArgs& a, int n_tiles, cudaStream_t stream) {
-  const size_t smem = LocalMmaSmem<DK, DV>::BYTES;
+  const size_t smem = a.v_cache == a.k_cache ? (size_t)2 * LocalMmaSmem<DK, DV>::KTILE * 2 : LocalMmaSmem<DK, DV>::BYTES;
   auto kernel = local_prefill_mma_kernel<DK, DV>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) {

@@ -80,8 +80,8 @@ def run_alone(llm, toks, cuts):
 
 
 LENGTH = {"sink_only": 150, "latent_only": 150, "routed": 75, "reentry": 75, "mixed": 200, "ones": 140, "wide": 135,
-          "odd": 90}
-ROUTED = {"routed", "mixed", "ones", "wide", "odd"}
+          "tensor": 300, "odd": 90}
+ROUTED = {"routed", "mixed", "ones", "wide", "tensor", "odd"}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -399,6 +399,59 @@ def test_single_token_kernel_with_heads_as_rows(H, G, d, dv, sink, v_in_k):
         err = (out.cpu().double() - want).abs()
         assert torch.isfinite(out.float()).all()
         assert err.max().item() <= 3e-2 * max(1.0, want.abs().max().item()), (splits, err.max().item(), int(err.argmax()) // (H * dv))
+
+
+@pytest.mark.parametrize("d", [32, 48, 64, 128])
+def test_sink_in_the_kernels_shared_with_the_other_decoders(d):
+    """Keys and values of one head size in bfloat16: prompts on the tcgen05 kernel (64, 128) and single tokens on the
+    TMA-fed (64, 128) or mma.sync decode kernel, each with the sink, against the general kernel with the sink; scores
+    are small, so the sink holds a large share of every row's denominator.  Decode runs with one block a sequence and
+    with the context split in four (the sink must be counted once)."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(d)
+    H, G = 4, 2
+    starts, lens = [0, 70, 129], [300, 200, 1]
+    ctxs = [s + n for s, n in zip(starts, lens)]
+    k_cache, v_cache, table = _paged(gen, ctxs, G, d, d, torch.bfloat16, dev)
+    k_cache, v_cache, table = k_cache.to(dev), v_cache.to(dev), table.to(dev)
+    scale = 0.5 / d ** 0.5
+    T = sum(lens)
+    q = torch.randn((T, H * d), generator=gen).to(torch.bfloat16).to(dev)
+    state = make_step_state(dev, [0, 1, 2], starts, lens)
+    plain = torch.zeros((T, H * d), dtype=torch.bfloat16, device=dev)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, plain, H, G, d, d, 0, 0, scale,
+                      sink=True)
+    without = torch.zeros_like(plain)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, without, H, G, d, d, 0, 0, scale)
+    torch.cuda.synchronize()
+    size = plain.float().abs().max().item()
+    assert (plain.float() - without.float()).abs().max().item() > 0.2 * size  # the sink matters in this test
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=dev)
+    if K.attention_prefill_takes_chunks(torch.bfloat16, d):
+        narrow = [(s, r) for s, n in enumerate(lens) for r in range(0, n, K.PREFILL_TILE)]
+        wide = sorted((starts[s] + min(n, r + 128), s, r) for s, n in enumerate(lens) for r in range(0, n, 128))
+        fast = torch.zeros_like(plain)
+        K.attention_prefill(q, k_cache, v_cache, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
+                            ints([s for s, _ in narrow]), ints([r for _, r in narrow]), table, fast, len(narrow), H, G, d, 0,
+                            scale, wide_tiles=(ints([s for _, s, _ in wide]), ints([r for _, _, r in wide])), sink=True)
+        torch.cuda.synchronize()
+        assert K.take_device_error() == 0
+        assert (fast.float() - plain.float()).abs().max().item() <= 0.03 * size
+    # single tokens: the last token of every sequence
+    last = [sum(lens[:i + 1]) - 1 for i in range(3)]
+    q1 = q[last].contiguous()
+    one = make_step_state(dev, [0, 1, 2], [c - 1 for c in ctxs], [1, 1, 1])
+    for splits in (1, 4):
+        out = torch.zeros((3, H * d), dtype=torch.bfloat16, device=dev)
+        scratch = torch.zeros((K.attention_decode_scratch_floats(3, H, d, splits),), device=dev) if splits > 1 else None
+        counters = torch.zeros((3 * G,), dtype=torch.int32, device=dev) if splits > 1 else None
+        K.attention_decode(q1, k_cache, v_cache, one.seq_slot, one.seq_ctx, table, scratch, out, 3, H, G, d, splits, 0, scale,
+                           counters=counters, sink=True)
+        torch.cuda.synchronize()
+        assert K.take_device_error() == 0
+        assert (out.float() - plain[last].float()).abs().max().item() <= 0.03 * size, splits
 
 
 @pytest.mark.parametrize("every,coef", [(1, 1.0), (5, 0.3), (64, 0.7)])

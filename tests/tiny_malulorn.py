@@ -62,6 +62,13 @@ CONFIGS = {
                             attention(heads=2, kv_heads=1, dim=72, vdim=136, temp=(0.2, 16), mlp=moe(9, 2, 72, 0)),
                             latent(heads=4, dim=32, rot_dim=64, vdim=32, kv_rank=136, mlp=None)],
                            width=64, vocab=50),
+    # head sizes of 64 and 128 for keys and values alike: in bfloat16 the sink layers run on the tcgen05 prompt kernel
+    # and the TMA-fed decode kernel, at 32 on the mma.sync decode kernel; a latent row of exactly 256
+    "tensor": lambda: config([attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.2, temp=(0.3, 32), mlp=moe(4, 2, 32, 16)),
+                              attention(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.15, temp=None, mlp=None),
+                              latent(heads=4, dim=32, rot_dim=64, vdim=32, kv_rank=192, scale=0.1, mlp=moe(8, 2, 64, 0)),
+                              attention(heads=4, kv_heads=4, dim=32, vdim=32, scale=0.3, temp=(0.5, 100), mlp=None)],
+                             width=128, vocab=89, loop=(0, 2, 2)),
     # nothing divisible by four: a width of 50, heads of 6 and 10, the kernels' scalar paths
     "odd": lambda: config([attention(heads=3, kv_heads=1, dim=6, vdim=10, temp=(0.4, 7), mlp=moe(5, 2, 30, 14)),
                            latent(heads=3, dim=6, rot_dim=2, vdim=10, kv_rank=10, mlp=moe(5, 4, 6, 0))],
