@@ -200,9 +200,88 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const DeltaT* __rest
     o[i] = from_float<OutT>((row_buf[i] - mean) * scale * weight[i] + (bias ? bias[i] : 0.f));
 }
 
+// The same with the row in registers (widths that are multiples of 4, up to 4 * NV * 256): every thread issues all its
+// loads before the first use, and the two passes (mean, then squared deviations) run over registers.
+template <typename DeltaT, typename OutT, int NV>
+__global__ void __launch_bounds__(256)
+add_layernorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta, const float* __restrict__ weight,
+                         const float* __restrict__ bias, OutT* __restrict__ out, const int* __restrict__ rows, int width,
+                         float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * width;
+  const DeltaT* dr = delta ? delta + (size_t)src * width : nullptr;
+  const int groups = width >> 2;
+  float4 v[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int g = threadIdx.x + k * 256;
+    v[k] = g < groups ? load4<float>(xr + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (dr) {
+    float4 dl[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int g = threadIdx.x + k * 256;
+      if (g < groups) dl[k] = load4<DeltaT>(dr + 4 * g);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int g = threadIdx.x + k * 256;
+      if (g < groups) {
+        v[k].x += dl[k].x; v[k].y += dl[k].y; v[k].z += dl[k].z; v[k].w += dl[k].w;
+        if (!rows) store4(xr + 4 * g, v[k]);
+      }
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);  // groups past the row hold zeros
+  const float mean = block_sum(sum, scratch) / (float)width;
+  float dev = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int g = threadIdx.x + k * 256;
+    if (g < groups) {
+      v[k].x -= mean; v[k].y -= mean; v[k].z -= mean; v[k].w -= mean;
+      dev += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    }
+  }
+  const float scale = 1.f / sqrtf(block_sum(dev, scratch) / (float)width + eps);
+  OutT* o = out + (size_t)r * width;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int g = threadIdx.x + k * 256;
+    if (g < groups) {
+      const float4 w = load4<float>(weight + 4 * g);
+      const float4 b = bias ? load4<float>(bias + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+      store4(o + 4 * g, make_float4(v[k].x * scale * w.x + b.x, v[k].y * scale * w.y + b.y, v[k].z * scale * w.z + b.z,
+                                    v[k].w * scale * w.w + b.w));
+    }
+  }
+}
+
 template <typename DeltaT, typename OutT>
 int launch_add_layernorm(float* x, const void* delta, const float* weight, const float* bias, void* out,
                          const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+  const bool aligned = width % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                       ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 8 == 0) &&
+                       (!bias || (uintptr_t)bias % 16 == 0);
+  if (aligned && width <= 4 * 256 * 8) {
+    const int groups = width / 4;
+    if (groups <= 256 * 2)
+      MLL_LAUNCH((add_layernorm_vec_kernel<DeltaT, OutT, 2>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight, bias,
+                 (OutT*)out, rows, width, eps);
+    else if (groups <= 256 * 4)
+      MLL_LAUNCH((add_layernorm_vec_kernel<DeltaT, OutT, 4>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight, bias,
+                 (OutT*)out, rows, width, eps);
+    else
+      MLL_LAUNCH((add_layernorm_vec_kernel<DeltaT, OutT, 8>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight, bias,
+                 (OutT*)out, rows, width, eps);
+    MLL_LAUNCH_CHECK();
+    return 0;
+  }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   const size_t smem = (size_t)width * sizeof(float);
   auto kernel = add_layernorm_kernel<DeltaT, OutT>;

@@ -545,7 +545,7 @@ def test_routed_feed_forward_kernels(dtype, T, E, top, D, F):
         assert err <= tol * max(1.0, want.abs().max().item()), (mma, small, err)
 
 
-@pytest.mark.parametrize("width", [40, 50, 256, 1000])
+@pytest.mark.parametrize("width", [40, 50, 256, 1000, 4096, 9000])
 def test_layer_norm_kernel(width):
     from cpp_minilamma_b200.csrc import kernels as K
     dev = torch.device("cuda:0")
