@@ -364,7 +364,7 @@ def test_attention_kernels_with_a_far_key_that_stands_out(dtype, d, dv, sink, v_
 
 
 @pytest.mark.parametrize("H,G,d,dv,sink,v_in_k", [(4, 2, 16, 24, True, False), (20, 1, 48, 32, False, True),
-                                                  (80, 1, 144, 128, False, True), (6, 3, 72, 136, True, False),
+                                                  (80, 1, 152, 136, False, True), (6, 3, 72, 136, True, False),
                                                   (8, 8, 64, 64, True, False), (3, 1, 256, 8, True, False)])
 def test_single_token_kernel_with_heads_as_rows(H, G, d, dv, sink, v_in_k):
     """Single tokens in bfloat16 on tensor cores, a kv head's query heads as the rows of a tile (more than 64 heads
