@@ -5,8 +5,8 @@
 // Eight warps as 4 x 2: a warp owns 32 of the tile's rows and 64 of its weight rows.  (Four warps on 64 rows, two blocks
 // a multiprocessor, kept the tensor pipe 43 % busy with an eighth of the warp slots filled.)
 // Steps with few rows per expert (single tokens) take a second instance: tiles of 16 rows - one MMA row tile - and
-// four warps side by side on 256 weight rows, four stages (two warps on 128 weight rows, two blocks a multiprocessor,
-// were a quarter slower).  Such a step streams every touched expert's weights once
+// four warps side by side on 64 weight rows, four stages, four such blocks a multiprocessor (256 weight rows, one
+// block a multiprocessor: the same time; two warps on 128 weight rows: a quarter slower).  Such a step streams every touched expert's weights once
 // for a handful of rows, and on the wide tile it was bound by the MMAs spent on empty rows (128-row tiles at batch 64:
 // 2 TB/s from a cold cache).
 //   gate_up  the 128 weight rows are 64 gate rows and the 64 up rows of the same activation columns; a warp's
@@ -21,19 +21,20 @@
 
 namespace mll {
 
-// WM x WN warps, each on 16 MT rows x 64 weight rows; BK columns of k a stage.  Rows of BK + 8 elements: ldmatrix
+// WM x WN warps, each on 16 MT rows x 8 NT weight rows; BK columns of k a stage.  Rows of BK + 8 elements: ldmatrix
 // without bank conflicts.
-template <int MT, int WM, int WN, int BK, int STAGES>
+template <int MT, int NT, int WM, int WN, int BK, int STAGES>
 struct MoeMmaShape {
-  static constexpr int BM = 16 * MT * WM, BN = 64 * WN, LD = BK + 8, THREADS = 32 * WM * WN;
+  static constexpr int BM = 16 * MT * WM, BN = 8 * NT * WN, LD = BK + 8, THREADS = 32 * WM * WN;
   static constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * LD * sizeof(__nv_bfloat16);
 };
-using MoeMmaWide = MoeMmaShape<2, 4, 2, 64, 3>;   // 128 rows: prompts
-using MoeMmaSmall = MoeMmaShape<1, 1, 4, 64, 4>;  // 16 rows: single tokens
+using MoeMmaWide = MoeMmaShape<2, 8, 4, 2, 64, 3>;   // 128 rows x 128 weight rows: prompts
+using MoeMmaSmall = MoeMmaShape<1, 2, 1, 4, 64, 4>;  // 16 rows x 64 weight rows: single tokens
 
-template <bool GATE_UP, int MT, int WM, int WN, int MMA_BK, int MMA_STAGES>
+template <bool GATE_UP, int MT, int NT, int WM, int WN, int MMA_BK, int MMA_STAGES>
 __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a) {
-  using Shape = MoeMmaShape<MT, WM, WN, MMA_BK, MMA_STAGES>;
+  using Shape = MoeMmaShape<MT, NT, WM, WN, MMA_BK, MMA_STAGES>;
+  static_assert(NT % 2 == 0, "a warp's 8-column tiles come in pairs");
   constexpr int BM = Shape::BM, BN = Shape::BN, MMA_LD = Shape::LD, MMA_THREADS = Shape::THREADS;
   const int tile = blockIdx.x;
   if (tile >= a.plan.n_tiles[0]) return;
@@ -73,11 +74,11 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
     }
   };
 
-  float acc[MT][8][4];
+  float acc[MT][NT][4];
 #pragma unroll
   for (int m = 0; m < MT; ++m)
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
 
@@ -100,11 +101,15 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
       for (int m = 0; m < MT; ++m)
         ldmatrix_x4(af[m], &a_s[stage][wm * 16 * MT + m * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)][ks * 16 + ((lane >> 4) << 3)]);
 #pragma unroll
-      for (int n = 0; n < 8; n += 2) {
-        // the warp's n-th 8-column tile: gate_up 0..3 gate, 4..7 up, both at columns wn * 32 + (n & 3) * 8
-        const int brow = GATE_UP ? (n >> 2) * (BN / 2) + wn * 32 + (n & 3) * 8 : wn * 64 + n * 8;
+      for (int n = 0; n < NT; n += 2) {
+        // the warp's n-th 8-column tile: gate_up: the first NT / 2 are gate, the others up, both at columns
+        // wn * 4 NT + (n mod NT / 2) * 8.  Tiles n and n + 1 come with one ldmatrix: they lie 8 rows apart, except
+        // where a warp has one gate and one up tile, which lie half the weight rows apart.
+        constexpr int HALF = NT / 2;
+        const int brow = GATE_UP ? (n / HALF) * (BN / 2) + wn * HALF * 8 + (n % HALF) * 8 : wn * NT * 8 + n * 8;
+        const int second = GATE_UP && NT == 2 ? BN / 2 : 8;
         unsigned bf[4];
-        ldmatrix_x4(bf, &b_s[stage][brow + (lane & 7) + ((lane >> 4) << 3)][ks * 16 + (((lane >> 3) & 1) << 3)]);
+        ldmatrix_x4(bf, &b_s[stage][brow + (lane & 7) + ((lane >> 4) ? second : 0)][ks * 16 + (((lane >> 3) & 1) << 3)]);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           mma_16816(acc[m][n], af[m], bf[0], bf[1]);
@@ -125,11 +130,11 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
       if (GATE_UP) {
         __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)place * N;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-          const int col = n0 + wn * 32 + n * 8 + 2 * t;
+        for (int n = 0; n < NT / 2; ++n) {
+          const int col = n0 + wn * (NT / 2) * 8 + n * 8 + 2 * t;
           if (col >= N) continue;  // N is even: a pair is inside or outside as a whole
           const float g0 = acc[m][n][2 * half], g1 = acc[m][n][2 * half + 1];
-          const float u0 = acc[m][n + 4][2 * half], u1 = acc[m][n + 4][2 * half + 1];
+          const float u0 = acc[m][n + NT / 2][2 * half], u1 = acc[m][n + NT / 2][2 * half + 1];
           *reinterpret_cast<__nv_bfloat162*>(dst + col) =
               __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
         }
@@ -138,8 +143,8 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
         const float pw = a.pair_weight[pair];
         float* dst = (float*)a.out + (size_t)pair * N;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const int col = n0 + wn * 64 + n * 8 + 2 * t;
+        for (int n = 0; n < NT; ++n) {
+          const int col = n0 + wn * NT * 8 + n * 8 + 2 * t;
           if (col >= N) continue;
           *reinterpret_cast<float2*>(dst + col) = make_float2(pw * acc[m][n][2 * half], pw * acc[m][n][2 * half + 1]);
         }
@@ -147,10 +152,10 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
     }
 }
 
-template <bool GATE_UP, int MT, int WM, int WN, int BK, int STAGES>
+template <bool GATE_UP, int MT, int NT, int WM, int WN, int BK, int STAGES>
 int launch_moe_mma(const MoeProductArgs& a, int max_tiles, cudaStream_t stream) {
-  using Shape = MoeMmaShape<MT, WM, WN, BK, STAGES>;
-  auto kernel = moe_mma_kernel<GATE_UP, MT, WM, WN, BK, STAGES>;
+  using Shape = MoeMmaShape<MT, NT, WM, WN, BK, STAGES>;
+  auto kernel = moe_mma_kernel<GATE_UP, MT, NT, WM, WN, BK, STAGES>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::SMEM);
   if (err != cudaSuccess) {
     mll_set_error("moe (mma): cannot reserve %zu bytes of shared memory: %s", Shape::SMEM, cudaGetErrorString(err));
@@ -164,8 +169,8 @@ int launch_moe_mma(const MoeProductArgs& a, int max_tiles, cudaStream_t stream) 
 
 template <bool GATE_UP>
 int launch_moe_mma_rows(const MoeProductArgs& a, int max_tiles, int tile_rows, cudaStream_t stream) {
-  if (tile_rows == MoeMmaWide::BM) return launch_moe_mma<GATE_UP, 2, 4, 2, 64, 3>(a, max_tiles, stream);
-  if (tile_rows == MoeMmaSmall::BM) return launch_moe_mma<GATE_UP, 1, 1, 4, 64, 4>(a, max_tiles, stream);
+  if (tile_rows == MoeMmaWide::BM) return launch_moe_mma<GATE_UP, 2, 8, 4, 2, 64, 3>(a, max_tiles, stream);
+  if (tile_rows == MoeMmaSmall::BM) return launch_moe_mma<GATE_UP, 1, 2, 1, 4, 64, 4>(a, max_tiles, stream);
   mll_set_error("moe (mma): tiles of %d rows (known: %d, %d)", tile_rows, MoeMmaSmall::BM, MoeMmaWide::BM);
   return -1;
 }
@@ -182,7 +187,7 @@ MLL_API int mll_moe_gate_up_mma(const void* h, const void* w, void* act, const i
                                 const int* tile_expert, const int* tile_row0, const int* n_tiles, int max_tiles,
                                 int tile_rows, int width, int inter, int top, cudaStream_t stream) {
   MLL_REQUIRE(mll_moe_mma_supported(width, inter) && max_tiles > 0 && top > 0, "moe gate_up (mma): sizes %d / %d", width, inter);
-  MLL_REQUIRE((inter + 63) / 64 <= 65535, "moe gate_up (mma): %d columns are too many for one launch", inter);
+  MLL_REQUIRE((inter + 31) / 32 <= 65535, "moe gate_up (mma): %d columns are too many for one launch", inter);
   mll::MoeProductArgs a{h, w, act, nullptr, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert, (int*)tile_row0,
                                                          (int*)n_tiles}, width, inter, top};
   return mll::launch_moe_mma_rows<true>(a, max_tiles, tile_rows, stream);
@@ -192,7 +197,7 @@ MLL_API int mll_moe_down_mma(const void* act, const void* w, float* y, const flo
                              const int* offsets, const int* tile_expert, const int* tile_row0, const int* n_tiles,
                              int max_tiles, int tile_rows, int inter, int width, int top, cudaStream_t stream) {
   MLL_REQUIRE(mll_moe_mma_supported(width, inter) && max_tiles > 0 && top > 0, "moe down (mma): sizes %d / %d", width, inter);
-  MLL_REQUIRE((width + 127) / 128 <= 65535, "moe down (mma): %d columns are too many for one launch", width);
+  MLL_REQUIRE((width + 63) / 64 <= 65535, "moe down (mma): %d columns are too many for one launch", width);
   mll::MoeProductArgs a{act, w, y, pair_weight, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert,
                                                              (int*)tile_row0, (int*)n_tiles}, inter, width, top};
   return mll::launch_moe_mma_rows<false>(a, max_tiles, tile_rows, stream);
